@@ -1,0 +1,87 @@
+"""Generate the golden fixtures by running the REFERENCE's own oracle.
+
+Run in a container where the reference checkout is mounted:
+
+    python tests/golden/make_golden.py /path/to/reference
+
+It imports ``attention.reference_gqa_decode`` (attention/reference/gqa.py:7-44)
+and the reference's fixture generator ``make_decode_case``
+(benchmarks/data.py:8-43) from that checkout, and writes
+
+  full_*.npz   small cases with every input stored next to the reference output
+  seed_*.npz   larger cases: only the generator arguments, a sha256 of the
+               regenerated inputs, and the reference output are stored; a test
+               regenerates the inputs from the seed, checks the digest, then
+               compares
+
+The reference is only needed to (re)generate; the tests read the .npz files.
+"""
+
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE))
+sys.path.insert(0, str(HERE.parents[1]))
+
+from golden_io import digest, to_np  # noqa: E402
+
+from attention_b200 import synth  # noqa: E402
+
+
+def main(ref_root: str) -> None:
+    sys.path.insert(0, ref_root)
+    sys.path.insert(0, str(Path(ref_root) / "benchmarks"))
+    from attention import reference_gqa_decode  # the reference's oracle
+    from data import make_decode_case           # the reference's fixture generator
+
+    torch.set_num_threads(8)
+
+    # ---- small cases, inputs stored in full (reference generator) ----------
+    full_cases = [
+        # name, lengths, q_heads, kv_heads, head_dim, block_size, dtype, seed, scale
+        ("full_f32_g3_d32_bs4", [0, 1, 3, 4, 5, 9], 6, 2, 32, 4, torch.float32, 42, None),
+        ("full_bf16_g4_d128_bs16", [40, 7, 64], 8, 2, 128, 16, torch.bfloat16, 7, None),
+        ("full_f16_g7_d128_bs16", [33, 16, 1], 7, 1, 128, 16, torch.float16, 11, None),
+        ("full_f16_mha_d64_bs8", [0, 17, 8, 23], 4, 4, 64, 8, torch.float16, 3, 0.2),
+        ("full_f32_mqa_d80_bs5", [12, 5, 6], 5, 1, 80, 5, torch.float32, 5, None),
+        ("full_bf16_g8_d256_bs32", [70, 32], 16, 2, 256, 32, torch.bfloat16, 9, None),
+    ]
+    for name, lengths, hq, hkv, d, bs, dtype, seed, scale in full_cases:
+        q, k, v, table, lens = make_decode_case(lengths=lengths, q_heads=hq, kv_heads=hkv,
+                                                head_dim=d, block_size=bs, dtype=dtype, seed=seed)
+        out = reference_gqa_decode(q, k, v, table, lens, scale=scale)
+        np.savez_compressed(
+            HERE / f"{name}.npz", q=to_np(q), k=to_np(k), v=to_np(v), table=to_np(table),
+            lens=to_np(lens), out=to_np(out), dtype=str(dtype).replace("torch.", ""),
+            scale=np.float64(-1.0 if scale is None else scale))
+        print(name, tuple(out.shape))
+
+    # ---- seeded cases (this library's workload generator) ------------------
+    seeded = [
+        ("seed_c1_cpu_fp32", synth.WORKLOADS["c1_cpu_fp32"], 42),
+        ("seed_c2_small_bf16", synth.scaled("c2_qwen3_8b_bf16", batch=3, len_lo=500, len_hi=1200), 42),
+        ("seed_c3_small_fp16", synth.scaled("c3_qwen25_7b_fp16", batch=4, len_lo=100, len_hi=700), 42),
+        ("seed_c4_small_bf16", synth.scaled("c4_longctx_bf16", batch=2, len_lo=3000, len_hi=5000), 42),
+        ("seed_c5_small_bf16", synth.scaled("c5_skewed_bf16", batch=12, len_hi=4096), 42),
+    ]
+    for name, w, seed in seeded:
+        q, k, v, table, lens = synth.make_workload(w, seed=seed)
+        out = reference_gqa_decode(q, k, v, table, lens)
+        np.savez_compressed(
+            HERE / f"{name}.npz", out=to_np(out), lens=to_np(lens),
+            dtype=str(w.dtype).replace("torch.", ""), seed=np.int64(seed),
+            digest=digest(q, k, v, table, lens),
+            workload=np.array([w.batch, w.q_heads, w.kv_heads, w.head_dim, w.block_size,
+                               w.len_lo, w.len_hi, w.fixed_pool_blocks], dtype=np.int64),
+            len_dist=w.len_dist)
+        print(name, tuple(out.shape), lens.tolist()[:8])
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
