@@ -1,0 +1,496 @@
+// C ABI of the B200 paged GQA decode library: argument checks, workspace
+// carving, kernel selection and launches.  No allocation, no synchronisation,
+// no exceptions cross this boundary.
+#include "../../include/gqa_decode_b200.h"
+
+#include <cmath>
+#include <cstdint>
+#include <limits>
+#include <mutex>
+
+#include "gqa_common.cuh"
+#include "gqa_decode_mma.cuh"
+#include "gqa_decode_simt.cuh"
+#include "gqa_plan_merge.cuh"
+#include "kv_append.cuh"
+
+using namespace gqa_b200;
+
+namespace {
+
+constexpr int kTableEntriesBudget = 2048;   // page ids staged in shared memory per segment
+constexpr int kMaxDevices = 64;
+
+struct DeviceInfo {
+    int sm_count = 0;
+    int max_smem_optin = 0;
+    bool ready = false;
+};
+DeviceInfo g_dev[kMaxDevices];
+
+// Device properties are read once per device (two cudaDeviceGetAttribute calls;
+// benign if two threads race to fill the same slot with the same values).
+cudaError_t device_info(DeviceInfo** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    DeviceInfo& d = g_dev[dev];
+    if (!d.ready) {
+        e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+        e = cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        if (e != cudaSuccess) return e;
+        d.ready = true;
+    }
+    *out = &d;
+    return cudaSuccess;
+}
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int elem_size(int dtype) { return dtype == GQA_B200_F32 ? 4 : 2; }
+
+struct WorkspaceLayout {
+    size_t hdr, chunk_off, items, part_ml, part_acc, total;
+    int cap_chunks;
+};
+
+WorkspaceLayout workspace_layout(int batch, int q_heads, int head_dim, int block_size,
+                                 int max_pages, int chunk_base) {
+    WorkspaceLayout w{};
+    const long long cap_tokens = (long long)max_pages * block_size;
+    const long long per_seq = max_chunks_for_capacity(cap_tokens, chunk_base);
+    long long cap = per_seq * (batch > 0 ? batch : 0);
+    if (cap > 0x7fffffffll) cap = 0x7fffffffll;
+    w.cap_chunks = (int)cap;
+    size_t at = 0;
+    w.hdr = at;        at = align_up(at + kHdrWords * sizeof(int32_t), 256);
+    w.chunk_off = at;  at = align_up(at + ((size_t)batch + 1) * sizeof(int32_t), 256);
+    w.items = at;      at = align_up(at + (size_t)cap * sizeof(int2), 256);
+    w.part_ml = at;    at = align_up(at + (size_t)cap * q_heads * sizeof(float2), 256);
+    w.part_acc = at;   at = align_up(at + (size_t)cap * q_heads * head_dim * sizeof(float), 256);
+    w.total = at;
+    return w;
+}
+
+int resolve_chunk_base(int chunk_tokens) {
+    if (chunk_tokens == 0) return kDefaultChunkTokens;
+    if (chunk_tokens < kMinChunkTokens || chunk_tokens > kMaxChunkTokens) return -1;
+    return chunk_tokens;
+}
+
+// The reference's argument checks (csrc/cuda/dense/gqa_decode.cu:103-138) that
+// can be made on sizes alone; dtype/device/contiguity of the tensors themselves
+// are the caller's (the Python wrapper's) to check.
+int check_common(const void* q, const void* k, const void* v, const int32_t* table,
+                 const int32_t* lens, const void* out, int dtype, int batch, int q_heads,
+                 int kv_heads, int head_dim, int64_t num_blocks, int block_size, int max_pages,
+                 float scale) {
+    if (dtype != GQA_B200_F32 && dtype != GQA_B200_F16 && dtype != GQA_B200_BF16)
+        return GQA_B200_ERR_DTYPE;
+    if (batch < 0) return GQA_B200_ERR_BATCH;
+    if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) return GQA_B200_ERR_HEADS;
+    if (head_dim <= 0 || head_dim > 256) return GQA_B200_ERR_HEAD_DIM;
+    if (num_blocks <= 0 || block_size <= 0) return GQA_B200_ERR_CACHE_SHAPE;
+    if (max_pages <= 0) return GQA_B200_ERR_MAX_PAGES;
+    if (!(std::isfinite(scale) && scale > 0.f)) return GQA_B200_ERR_SCALE;
+    if (num_blocks > std::numeric_limits<int>::max()) return GQA_B200_ERR_INT32_RANGE;
+    if ((long long)batch * q_heads > std::numeric_limits<int>::max())
+        return GQA_B200_ERR_INT32_RANGE;
+    if (batch > 0 && (!q || !k || !v || !table || !lens || !out)) return GQA_B200_ERR_NULL_POINTER;
+    return GQA_B200_OK;
+}
+
+void fill_shape(DecodeParams& p, const void* q, const void* k, const void* v,
+                const int32_t* table, const int32_t* lens, void* out, int batch, int q_heads,
+                int kv_heads, int head_dim, int64_t num_blocks, int block_size, int max_pages,
+                float scale) {
+    p.q = q; p.k = k; p.v = v; p.out = out; p.table = table; p.lens = lens;
+    p.batch = batch; p.q_heads = q_heads; p.kv_heads = kv_heads; p.group = q_heads / kv_heads;
+    p.head_dim = head_dim;
+    p.block_size = block_size;
+    p.bs_shift = -1;
+    if ((block_size & (block_size - 1)) == 0) {
+        int s = 0;
+        while ((1 << s) < block_size) ++s;
+        p.bs_shift = s;
+    }
+    p.max_pages = max_pages;
+    p.num_blocks = num_blocks;
+    const long long cap = (long long)max_pages * block_size;
+    p.cap_tokens = cap > 0x7fffffffll ? 0x7fffffff : (int)cap;
+    p.scale_log2 = scale * kLog2e;
+}
+
+void set_segment(DecodeParams& p, long long max_part_tokens) {
+    long long seg = (long long)kTableEntriesBudget * p.block_size;
+    if (seg > max_part_tokens) seg = max_part_tokens;
+    if (seg < 1) seg = 1;
+    if (seg > 0x40000000ll) seg = 0x40000000ll;
+    p.seg_tokens = (int)seg;
+    p.table_smem_entries = (int)(seg / p.block_size) + 2;
+}
+
+bool mma_eligible(const DecodeParams& p, int dtype) {
+    if (dtype == GQA_B200_F32) return false;
+    if (p.head_dim != 64 && p.head_dim != 128 && p.head_dim != 256) return false;
+    return aligned16(p.q) && aligned16(p.k) && aligned16(p.v) && aligned16(p.out);
+}
+
+// ---------------------------------------------------------------------------
+// launchers
+// ---------------------------------------------------------------------------
+// Resident CTAs per SM of a (kernel, dynamic shared memory) pair on a device.
+// Looked up on every call, computed once: the first use also raises the
+// kernel's dynamic shared-memory limit.
+struct OccEntry {
+    const void* kernel;
+    int dev;
+    size_t smem;
+    int per_sm;
+};
+constexpr int kOccEntries = 256;
+OccEntry g_occ[kOccEntries];
+int g_occ_count = 0;
+std::mutex g_occ_mutex;
+
+template <typename KernelT>
+cudaError_t resident_ctas(KernelT kernel, int threads, size_t smem, int smem_limit, int* per_sm) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const void* key = reinterpret_cast<const void*>(kernel);
+    std::lock_guard<std::mutex> lock(g_occ_mutex);
+    for (int i = 0; i < g_occ_count; ++i) {
+        if (g_occ[i].kernel == key && g_occ[i].dev == dev && g_occ[i].smem == smem) {
+            *per_sm = g_occ[i].per_sm;
+            return cudaSuccess;
+        }
+    }
+    // raise the limit to the device maximum once, so later calls with another
+    // table size never lower it
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_limit);
+    if (e != cudaSuccess) return e;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, kernel, threads, smem);
+    if (e != cudaSuccess) return e;
+    if (g_occ_count < kOccEntries) g_occ[g_occ_count++] = OccEntry{key, dev, smem, *per_sm};
+    return cudaSuccess;
+}
+
+template <typename KernelT>
+cudaError_t launch_persistent(KernelT kernel, const DecodeParams& p, int threads, size_t smem,
+                              int max_ctas, long long item_bound, cudaStream_t stream) {
+    DeviceInfo* dev = nullptr;
+    cudaError_t e = device_info(&dev);
+    if (e != cudaSuccess) return e;
+    if (smem > (size_t)dev->max_smem_optin) return cudaErrorInvalidValue;
+    int per_sm = 0;
+    e = resident_ctas(kernel, threads, smem, dev->max_smem_optin, &per_sm);
+    if (e != cudaSuccess) return e;
+    if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+    long long grid = (long long)per_sm * dev->sm_count;
+    if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+    if (grid > item_bound) grid = item_bound;
+    if (grid < 1) grid = 1;
+    kernel<<<(unsigned)grid, threads, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <typename T, int D, int TILE_N, int NSTAGES, int MIN_CTAS>
+cudaError_t launch_mma(const DecodeParams& p, int max_ctas, long long item_bound,
+                       cudaStream_t stream) {
+    constexpr int NWARPS = 4;
+    using G = MmaGeom<D, TILE_N, NSTAGES, NWARPS>;
+    const size_t smem = G::kFixedBytes + (size_t)p.table_smem_entries * sizeof(int);
+    return launch_persistent(gqa_decode_mma_kernel<T, D, TILE_N, NSTAGES, NWARPS, MIN_CTAS>, p,
+                             NWARPS * 32, smem, max_ctas, item_bound, stream);
+}
+
+template <typename T>
+cudaError_t launch_mma_for_dim(const DecodeParams& p, int max_ctas, long long item_bound,
+                               cudaStream_t stream) {
+    switch (p.head_dim) {
+        case 64:  return launch_mma<T, 64, 32, 3, 2>(p, max_ctas, item_bound, stream);
+        case 128: return launch_mma<T, 128, 16, 3, 2>(p, max_ctas, item_bound, stream);
+        case 256: return launch_mma<T, 256, 16, 3, 1>(p, max_ctas, item_bound, stream);
+        default:  return cudaErrorInvalidValue;
+    }
+}
+
+template <typename T, int EPL, bool CONTIG, int GB>
+cudaError_t launch_simt(const DecodeParams& p, int max_ctas, long long item_bound,
+                        cudaStream_t stream) {
+    const int o_stride = ((p.head_dim + 3) & ~3) + 4;
+    const size_t smem = ((size_t)kSimtWarps * GB * o_stride + 2 * kSimtWarps * GB) * sizeof(float) +
+                        (size_t)p.table_smem_entries * sizeof(int);
+    return launch_persistent(gqa_decode_simt_kernel<T, EPL, CONTIG, GB>, p, kSimtWarps * 32, smem,
+                             max_ctas, item_bound, stream);
+}
+
+// Query heads handled per SIMT item (registers: GB * EPL fp32 for q and for acc).
+inline int simt_heads_per_item(int head_dim, int group) {
+    const int epl = (head_dim + 31) / 32;
+    if (epl > 4) return 4;
+    return group > 4 ? 8 : 4;
+}
+
+template <typename T, int EPL, bool CONTIG>
+cudaError_t launch_simt_gb(const DecodeParams& p, int max_ctas, long long item_bound,
+                           cudaStream_t stream) {
+    if constexpr (EPL <= 4) {
+        if (p.heads_per_item == 8)
+            return launch_simt<T, EPL, CONTIG, 8>(p, max_ctas, item_bound, stream);
+    }
+    return launch_simt<T, EPL, CONTIG, 4>(p, max_ctas, item_bound, stream);
+}
+
+template <typename T>
+cudaError_t launch_simt_for_dim(const DecodeParams& p, int max_ctas, long long item_bound,
+                                cudaStream_t stream) {
+    const int D = p.head_dim;
+    const bool contig = (D % 32 == 0) && aligned16(p.q) && aligned16(p.k) && aligned16(p.v) &&
+                        aligned16(p.out);
+    const int epl = (D + 31) / 32;
+    if (contig) {
+        switch (epl) {
+            case 1: return launch_simt_gb<T, 1, true>(p, max_ctas, item_bound, stream);
+            case 2: return launch_simt_gb<T, 2, true>(p, max_ctas, item_bound, stream);
+            case 4: return launch_simt_gb<T, 4, true>(p, max_ctas, item_bound, stream);
+            case 8: return launch_simt_gb<T, 8, true>(p, max_ctas, item_bound, stream);
+            default: break;   // 96, 160, 192, 224: strided path below
+        }
+    }
+    if (epl <= 1) return launch_simt_gb<T, 1, false>(p, max_ctas, item_bound, stream);
+    if (epl <= 2) return launch_simt_gb<T, 2, false>(p, max_ctas, item_bound, stream);
+    if (epl <= 4) return launch_simt_gb<T, 4, false>(p, max_ctas, item_bound, stream);
+    return launch_simt_gb<T, 8, false>(p, max_ctas, item_bound, stream);
+}
+
+template <typename T>
+cudaError_t launch_decode_t(DecodeParams& p, bool use_mma, int max_ctas, cudaStream_t stream) {
+    if (use_mma) {
+        p.heads_per_item = 16;
+    } else {
+        p.heads_per_item = simt_heads_per_item(p.head_dim, p.group);
+    }
+    p.head_groups = (p.group + p.heads_per_item - 1) / p.heads_per_item;
+    long long parts = p.mode == kModePlanned ? (long long)p.cap_chunks
+                                             : (long long)p.batch * p.splits;
+    long long item_bound = parts * p.kv_heads * p.head_groups;
+    if (item_bound > 0x7fffffffll) return cudaErrorInvalidValue;
+    if (use_mma) {
+        if constexpr (sizeof(T) == 2) {
+            return launch_mma_for_dim<T>(p, max_ctas, item_bound, stream);
+        } else {
+            return cudaErrorInvalidValue;
+        }
+    }
+    return launch_simt_for_dim<T>(p, max_ctas, item_bound, stream);
+}
+
+cudaError_t launch_decode(DecodeParams& p, int dtype, bool use_mma, int max_ctas,
+                          cudaStream_t stream) {
+    switch (dtype) {
+        case GQA_B200_F32:  return launch_decode_t<float>(p, use_mma, max_ctas, stream);
+        case GQA_B200_F16:  return launch_decode_t<__half>(p, use_mma, max_ctas, stream);
+        default:            return launch_decode_t<__nv_bfloat16>(p, use_mma, max_ctas, stream);
+    }
+}
+
+template <typename T>
+cudaError_t launch_merge_t(const DecodeParams& p, cudaStream_t stream) {
+    const dim3 grid((unsigned)p.q_heads, (unsigned)p.batch);
+    const bool vec4 = p.mode == kModePlanned && p.head_dim % 4 == 0;
+    if (vec4) gqa_merge_kernel<T, true><<<grid, kMergeWarps * 32, 0, stream>>>(p);
+    else gqa_merge_kernel<T, false><<<grid, kMergeWarps * 32, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_merge(const DecodeParams& p, int dtype, cudaStream_t stream) {
+    switch (dtype) {
+        case GQA_B200_F32:  return launch_merge_t<float>(p, stream);
+        case GQA_B200_F16:  return launch_merge_t<__half>(p, stream);
+        default:            return launch_merge_t<__nv_bfloat16>(p, stream);
+    }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// exported entry points
+// ---------------------------------------------------------------------------
+extern "C" {
+
+int gqa_b200_abi_version(void) { return GQA_B200_ABI_VERSION; }
+
+const char* gqa_b200_strerror(int code) {
+    switch (code) {
+        case GQA_B200_OK: return "ok";
+        case GQA_B200_ERR_NULL_POINTER: return "a required pointer is null";
+        case GQA_B200_ERR_DTYPE: return "q/k/v must be float32/float16/bfloat16";
+        case GQA_B200_ERR_HEADS: return "Hq must be divisible by Hkv";
+        case GQA_B200_ERR_HEAD_DIM: return "supported head_dim is [1, 256]";
+        case GQA_B200_ERR_CACHE_SHAPE: return "cache must have positive blocks and block_size";
+        case GQA_B200_ERR_MAX_PAGES: return "block_table must have at least one page";
+        case GQA_B200_ERR_SCALE: return "scale must be positive and finite";
+        case GQA_B200_ERR_BATCH: return "batch must be non-negative";
+        case GQA_B200_ERR_WORKSPACE: return "workspace is missing, not 256-byte aligned, or too small";
+        case GQA_B200_ERR_SPLITS: return "splits must be in [1, 65535]";
+        case GQA_B200_ERR_KERNEL: return "the requested kernel cannot run these arguments";
+        case GQA_B200_ERR_CHUNK: return "chunk_tokens must be 0 or in [16, 65536]";
+        case GQA_B200_ERR_INT32_RANGE: return "tensor sizes exceed int32 CUDA launch limits";
+        default: break;
+    }
+    if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+    return "unknown gqa_b200 status";
+}
+
+int gqa_b200_chunk_tokens(int context_len, int chunk_tokens) {
+    const int base = resolve_chunk_base(chunk_tokens);
+    if (base < 0) return GQA_B200_ERR_CHUNK;
+    return chunk_tokens_for(context_len < 0 ? 0 : context_len, base);
+}
+
+int gqa_b200_max_chunks_per_seq(int max_pages, int block_size, int chunk_tokens) {
+    const int base = resolve_chunk_base(chunk_tokens);
+    if (base < 0) return GQA_B200_ERR_CHUNK;
+    if (max_pages <= 0 || block_size <= 0) return 0;
+    return max_chunks_for_capacity((long long)max_pages * block_size, base);
+}
+
+size_t gqa_b200_workspace_bytes(int batch, int q_heads, int head_dim, int block_size,
+                                int max_pages, int chunk_tokens) {
+    const int base = resolve_chunk_base(chunk_tokens);
+    if (base < 0 || batch < 0 || q_heads <= 0 || head_dim <= 0 || block_size <= 0 || max_pages <= 0)
+        return 0;
+    return workspace_layout(batch, q_heads, head_dim, block_size, max_pages, base).total;
+}
+
+int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
+                       const int32_t* block_table, const int32_t* context_lens, void* out,
+                       int dtype, int batch, int q_heads, int kv_heads, int head_dim,
+                       int64_t num_blocks, int block_size, int max_pages, float scale,
+                       void* workspace, size_t workspace_bytes, void* stream, int chunk_tokens,
+                       int kernel, int max_ctas, int phases) {
+    int rc = check_common(q, k_cache, v_cache, block_table, context_lens, out, dtype, batch,
+                          q_heads, kv_heads, head_dim, num_blocks, block_size, max_pages, scale);
+    if (rc != GQA_B200_OK) return rc;
+    const int base = resolve_chunk_base(chunk_tokens);
+    if (base < 0) return GQA_B200_ERR_CHUNK;
+    if (kernel != GQA_B200_KERNEL_AUTO && kernel != GQA_B200_KERNEL_SIMT &&
+        kernel != GQA_B200_KERNEL_MMA)
+        return GQA_B200_ERR_KERNEL;
+    if (batch == 0) return GQA_B200_OK;
+
+    const WorkspaceLayout lay = workspace_layout(batch, q_heads, head_dim, block_size, max_pages, base);
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < lay.total)
+        return GQA_B200_ERR_WORKSPACE;
+
+    DecodeParams p{};
+    fill_shape(p, q, k_cache, v_cache, block_table, context_lens, out, batch, q_heads, kv_heads,
+               head_dim, num_blocks, block_size, max_pages, scale);
+    char* ws = static_cast<char*>(workspace);
+    p.hdr = reinterpret_cast<int32_t*>(ws + lay.hdr);
+    p.chunk_off = reinterpret_cast<int32_t*>(ws + lay.chunk_off);
+    p.items = reinterpret_cast<int2*>(ws + lay.items);
+    p.part_ml = reinterpret_cast<float2*>(ws + lay.part_ml);
+    p.part_acc = reinterpret_cast<float*>(ws + lay.part_acc);
+    p.cap_chunks = lay.cap_chunks;
+    p.mode = kModePlanned;
+    p.splits = 1;
+    p.chunk_base = base;
+    set_segment(p, 4ll * base);
+
+    bool use_mma = mma_eligible(p, dtype);
+    if (kernel == GQA_B200_KERNEL_MMA && !use_mma) return GQA_B200_ERR_KERNEL;
+    if (kernel == GQA_B200_KERNEL_SIMT) use_mma = false;
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (phases == 0) phases = GQA_B200_PHASE_PLAN | GQA_B200_PHASE_DECODE | GQA_B200_PHASE_MERGE;
+    cudaError_t e = cudaSuccess;
+    if (phases & GQA_B200_PHASE_PLAN) {
+        gqa_plan_kernel<<<1, kPlanThreads, 0, s>>>(p);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (phases & GQA_B200_PHASE_DECODE) {
+        e = launch_decode(p, dtype, use_mma, max_ctas, s);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (phases & GQA_B200_PHASE_MERGE) e = launch_merge(p, dtype, s);
+    return (int)e;
+}
+
+int gqa_b200_decode(const void* q, const void* k_cache, const void* v_cache,
+                    const int32_t* block_table, const int32_t* context_lens, void* out, int dtype,
+                    int batch, int q_heads, int kv_heads, int head_dim, int64_t num_blocks,
+                    int block_size, int max_pages, float scale, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+    return gqa_b200_decode_ex(q, k_cache, v_cache, block_table, context_lens, out, dtype, batch,
+                              q_heads, kv_heads, head_dim, num_blocks, block_size, max_pages, scale,
+                              workspace, workspace_bytes, stream, 0, GQA_B200_KERNEL_AUTO, 0, 0);
+}
+
+int gqa_b200_decode_split(const void* q, const void* k_cache, const void* v_cache,
+                          const int32_t* block_table, const int32_t* context_lens, void* out,
+                          int dtype, int batch, int q_heads, int kv_heads, int head_dim,
+                          int64_t num_blocks, int block_size, int max_pages, float scale,
+                          int splits, float* partials, void* stream) {
+    if (splits < 1 || splits > 65535) return GQA_B200_ERR_SPLITS;
+    int rc = check_common(q, k_cache, v_cache, block_table, context_lens, out, dtype, batch,
+                          q_heads, kv_heads, head_dim, num_blocks, block_size, max_pages, scale);
+    if (rc != GQA_B200_OK) return rc;
+    if (batch == 0) return GQA_B200_OK;
+    if (splits > 1 && !partials) return GQA_B200_ERR_WORKSPACE;
+
+    DecodeParams p{};
+    fill_shape(p, q, k_cache, v_cache, block_table, context_lens, out, batch, q_heads, kv_heads,
+               head_dim, num_blocks, block_size, max_pages, scale);
+    p.mode = kModeRefSplits;
+    p.splits = splits;
+    p.ref_partials = partials;
+    p.chunk_base = kDefaultChunkTokens;
+    p.cap_chunks = 0;
+    set_segment(p, p.cap_tokens);
+
+    const bool use_mma = mma_eligible(p, dtype);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = launch_decode(p, dtype, use_mma, 0, s);
+    if (e != cudaSuccess) return (int)e;
+    if (splits > 1) e = launch_merge(p, dtype, s);
+    return (int)e;
+}
+
+int gqa_b200_kv_append(const void* key, const void* value, void* k_cache, void* v_cache,
+                       const int32_t* block_table, const int32_t* positions, int dtype, int batch,
+                       int kv_heads, int head_dim, int64_t num_blocks, int block_size,
+                       int max_pages, void* stream) {
+    if (dtype != GQA_B200_F32 && dtype != GQA_B200_F16 && dtype != GQA_B200_BF16)
+        return GQA_B200_ERR_DTYPE;
+    if (batch < 0) return GQA_B200_ERR_BATCH;
+    if (kv_heads <= 0) return GQA_B200_ERR_HEADS;
+    if (head_dim <= 0) return GQA_B200_ERR_HEAD_DIM;
+    if (num_blocks <= 0 || block_size <= 0) return GQA_B200_ERR_CACHE_SHAPE;
+    if (max_pages <= 0) return GQA_B200_ERR_MAX_PAGES;
+    if (num_blocks > std::numeric_limits<int>::max()) return GQA_B200_ERR_INT32_RANGE;
+    if (batch == 0) return GQA_B200_OK;
+    if (!key || !value || !k_cache || !v_cache || !block_table || !positions)
+        return GQA_B200_ERR_NULL_POINTER;
+    AppendParams a{};
+    a.key = key; a.value = value; a.k_cache = k_cache; a.v_cache = v_cache;
+    a.table = block_table; a.positions = positions;
+    a.row_bytes = (long long)kv_heads * head_dim * elem_size(dtype);
+    a.block_size = block_size; a.max_pages = max_pages; a.num_blocks = num_blocks;
+    const long long cap = (long long)max_pages * block_size;
+    a.cap_tokens = cap > 0x7fffffffll ? 0x7fffffff : (int)cap;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool vec = a.row_bytes % 16 == 0 && aligned16(key) && aligned16(value) &&
+                     aligned16(k_cache) && aligned16(v_cache);
+    if (vec) kv_append_kernel<uint4><<<batch, kAppendThreads, 0, s>>>(a);
+    else if (elem_size(dtype) == 4) kv_append_kernel<uint32_t><<<batch, kAppendThreads, 0, s>>>(a);
+    else kv_append_kernel<uint16_t><<<batch, kAppendThreads, 0, s>>>(a);
+    return (int)cudaGetLastError();
+}
+
+}  // extern "C"

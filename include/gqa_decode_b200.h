@@ -1,0 +1,158 @@
+/*
+ * gqa_decode_b200.h -- C ABI of the B200 (sm_100a) paged grouped-query decode library.
+ *
+ * Every entry point takes plain pointers and sizes, never allocates or frees
+ * device memory, never synchronises the device, never throws, and returns an
+ * int status: 0 = ok, < 0 = invalid argument (see gqa_b200_strerror), > 0 = a
+ * cudaError_t raised by a launch.  All device pointers must belong to the
+ * device that is current in the calling thread; work is enqueued on `stream`
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream).
+ *
+ * Tensor layouts are those of the reference library's operator
+ * (csrc/cuda/dense/gqa_decode.cu:109-113), all contiguous:
+ *   q, out        [batch, q_heads, head_dim]
+ *   k/v_cache     [num_blocks, block_size, kv_heads, head_dim]
+ *   block_table   [batch, max_pages] int32; slots past a sequence's used pages
+ *                 are never read and may hold -1
+ *   context_lens  [batch] int32
+ */
+#ifndef GQA_DECODE_B200_H
+#define GQA_DECODE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GQA_B200_API __attribute__((visibility("default")))
+
+#define GQA_B200_ABI_VERSION 1
+
+/* element types of q / k_cache / v_cache / out */
+#define GQA_B200_F32 0
+#define GQA_B200_F16 1
+#define GQA_B200_BF16 2
+
+/* kernel selection for gqa_b200_decode_ex */
+#define GQA_B200_KERNEL_AUTO 0 /* tensor-core kernel when eligible, else SIMT   */
+#define GQA_B200_KERNEL_SIMT 1 /* warp dot products + shuffle reductions, any D */
+#define GQA_B200_KERNEL_MMA 2  /* mma.sync m16n8k16; fp16/bf16, D in {64,128,256},
+                                  16-byte aligned tensors                        */
+
+/* status codes (negative = invalid argument) */
+#define GQA_B200_OK 0
+#define GQA_B200_ERR_NULL_POINTER (-1)
+#define GQA_B200_ERR_DTYPE (-2)       /* q/k/v must be float32/float16/bfloat16 */
+#define GQA_B200_ERR_HEADS (-3)       /* Hq must be divisible by Hkv            */
+#define GQA_B200_ERR_HEAD_DIM (-4)    /* supported head_dim is [1, 256]         */
+#define GQA_B200_ERR_CACHE_SHAPE (-5) /* cache must have positive blocks and block_size */
+#define GQA_B200_ERR_MAX_PAGES (-6)   /* block_table must have at least one page */
+#define GQA_B200_ERR_SCALE (-7)       /* scale must be positive and finite      */
+#define GQA_B200_ERR_BATCH (-8)       /* negative batch                         */
+#define GQA_B200_ERR_WORKSPACE (-9)   /* workspace missing, misaligned or too small */
+#define GQA_B200_ERR_SPLITS (-10)     /* splits must be in [1, 65535]           */
+#define GQA_B200_ERR_KERNEL (-11)     /* requested kernel cannot run these arguments */
+#define GQA_B200_ERR_CHUNK (-12)      /* chunk_tokens out of range              */
+#define GQA_B200_ERR_INT32_RANGE (-13)/* tensor sizes exceed int32 launch limits */
+
+/* Workspace header: the first int32 words of the workspace, readable by the
+ * host after a stream synchronise when debugging.
+ *   word 0  work-item counter of the last launch
+ *   word 1  number of (sequence, chunk) pairs the last plan produced
+ *   word 2  device status: 0 ok, 1 = plan overflowed the workspace (cannot
+ *           happen when it is sized by gqa_b200_workspace_bytes)            */
+#define GQA_B200_HDR_COUNTER 0
+#define GQA_B200_HDR_TOTAL_CHUNKS 1
+#define GQA_B200_HDR_STATUS 2
+
+GQA_B200_API int gqa_b200_abi_version(void);
+
+/* Text for a status code returned by any entry point (static storage). */
+GQA_B200_API const char* gqa_b200_strerror(int code);
+
+/* KV-chunk length, in tokens, that a sequence of `context_len` tokens is cut
+ * into.  A function of the sequence's own length only (so a sequence is cut the
+ * same way whichever batch or GPU it lands on).  chunk_tokens = 0 picks the
+ * built-in base.  Long sequences use 2x and 4x the base. */
+GQA_B200_API int gqa_b200_chunk_tokens(int context_len, int chunk_tokens);
+
+/* Upper bound on chunks per sequence for a table of max_pages*block_size tokens. */
+GQA_B200_API int gqa_b200_max_chunks_per_seq(int max_pages, int block_size, int chunk_tokens);
+
+/* Bytes of device scratch gqa_b200_decode / _decode_ex need for this static
+ * shape (worst case over context_lens).  The buffer must be 256-byte aligned.
+ * Its contents need no initialisation and carry nothing between calls; two
+ * calls that may overlap on the device need two workspaces. */
+GQA_B200_API size_t gqa_b200_workspace_bytes(int batch, int q_heads, int head_dim, int block_size,
+                                             int max_pages, int chunk_tokens);
+
+/* Paged single-token MHA/MQA/GQA decode.
+ * Replaces gqa_decode_cuda (csrc/binding/torch_ops.cpp:5-11,
+ * csrc/cuda/dense/gqa_decode.cu:186-188) and, through it, gqa_decode_impl
+ * (gqa_decode.cu:96-183) with its two kernels (gqa_decode.cu:18-87).
+ * Three launches on `stream`: plan (cuts sequences into KV chunks on the
+ * device, no host read of context_lens), decode (persistent CTAs pull
+ * (sequence, chunk, kv head) items; every K/V row is read once for all query
+ * heads of its group), merge (log-sum-exp fold of the chunk partials; also
+ * writes the zero rows of empty sequences).
+ * batch == 0 returns OK without launching (gqa_decode.cu:142). */
+GQA_B200_API int gqa_b200_decode(const void* q, const void* k_cache, const void* v_cache,
+                                 const int32_t* block_table, const int32_t* context_lens,
+                                 void* out, int dtype, int batch, int q_heads, int kv_heads,
+                                 int head_dim, int64_t num_blocks, int block_size, int max_pages,
+                                 float scale, void* workspace, size_t workspace_bytes,
+                                 void* stream);
+
+/* phases of gqa_b200_decode_ex (bit mask; 0 = all three) */
+#define GQA_B200_PHASE_PLAN 1
+#define GQA_B200_PHASE_DECODE 2
+#define GQA_B200_PHASE_MERGE 4
+
+/* Same operator with explicit tuning knobs (tests, benchmarks):
+ *   chunk_tokens  base KV-chunk length (0 = built-in; otherwise 16..65536)
+ *   kernel        GQA_B200_KERNEL_*
+ *   max_ctas      cap on the persistent grid (0 = SM count x resident CTAs)
+ *   phases        which of the three launches to enqueue (GQA_B200_PHASE_*;
+ *                 0 = all).  A benchmark uses it to put its own events around
+ *                 the decode kernel; the phases of one call must still run in
+ *                 order plan, decode, merge on the same workspace.            */
+GQA_B200_API int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
+                                    const int32_t* block_table, const int32_t* context_lens,
+                                    void* out, int dtype, int batch, int q_heads, int kv_heads,
+                                    int head_dim, int64_t num_blocks, int block_size,
+                                    int max_pages, float scale, void* workspace,
+                                    size_t workspace_bytes, void* stream, int chunk_tokens,
+                                    int kernel, int max_ctas, int phases);
+
+/* Decode with a caller-chosen number of KV partitions and the reference's
+ * partial layout.  Replaces gqa_decode_split_cuda and
+ * gqa_decode_split_workspace_cuda (csrc/cuda/dense/gqa_decode.cu:189-195):
+ * partition z of a sequence of length L covers tokens [L*z/splits, L*(z+1)/splits)
+ * (gqa_decode.cu:40-41); `partials` is float32 [batch, q_heads, splits, head_dim+2]
+ * holding [max, sum, acc...] per partition (gqa_decode.cu:67-69) and is
+ * overwritten; it is required when splits > 1 and ignored when splits == 1. */
+GQA_B200_API int gqa_b200_decode_split(const void* q, const void* k_cache, const void* v_cache,
+                                       const int32_t* block_table, const int32_t* context_lens,
+                                       void* out, int dtype, int batch, int q_heads, int kv_heads,
+                                       int head_dim, int64_t num_blocks, int block_size,
+                                       int max_pages, float scale, int splits, float* partials,
+                                       void* stream);
+
+/* Write one new token per sequence into its page.  Replaces kv_append_cuda
+ * (csrc/cuda/cache/kv_append.cu:29-56): key/value are [batch, kv_heads,
+ * head_dim]; the row goes to block_table[b, positions[b] / block_size], slot
+ * positions[b] % block_size.  The caller owns distinct, valid destinations.
+ * A position outside [0, max_pages*block_size) or a page id outside
+ * [0, num_blocks) is skipped (the reference reads out of bounds there). */
+GQA_B200_API int gqa_b200_kv_append(const void* key, const void* value, void* k_cache,
+                                    void* v_cache, const int32_t* block_table,
+                                    const int32_t* positions, int dtype, int batch, int kv_heads,
+                                    int head_dim, int64_t num_blocks, int block_size,
+                                    int max_pages, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GQA_DECODE_B200_H */
