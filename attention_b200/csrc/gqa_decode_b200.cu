@@ -168,9 +168,14 @@ cudaError_t resident_ctas(KernelT kernel, int threads, size_t smem, int smem_lim
             return cudaSuccess;
         }
     }
-    // raise the limit to the device maximum once, so later calls with another
-    // table size never lower it
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_limit);
+    // raise the dynamic limit to the device maximum (less the kernel's static
+    // shared memory) once, so later calls with another table size never lower it
+    cudaFuncAttributes fa{};
+    e = cudaFuncGetAttributes(&fa, kernel);
+    if (e != cudaSuccess) return e;
+    const int dyn_limit = smem_limit - (int)fa.sharedSizeBytes;
+    if ((long long)smem > dyn_limit) return cudaErrorInvalidValue;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_limit);
     if (e != cudaSuccess) return e;
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, kernel, threads, smem);
     if (e != cudaSuccess) return e;
