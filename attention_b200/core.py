@@ -91,9 +91,9 @@ def _stream_handle(device: torch.device) -> int:
     return int(torch.cuda.current_stream(device).cuda_stream)
 
 
-def _workspace_for(lib, q, block_size, max_pages, chunk_tokens, stream):
-    need = int(lib.gqa_b200_workspace_bytes(q.size(0), q.size(1), q.size(2), block_size, max_pages,
-                                            chunk_tokens))
+def _workspace_for(lib, q, kv_heads, block_size, max_pages, chunk_tokens, stream):
+    need = int(lib.gqa_b200_workspace_bytes(q.size(0), q.size(1), kv_heads, q.size(2), block_size,
+                                            max_pages, chunk_tokens))
     key = (q.device.index, stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < need:
@@ -102,10 +102,10 @@ def _workspace_for(lib, q, block_size, max_pages, chunk_tokens, stream):
     return ws, need
 
 
-def workspace_bytes(batch, q_heads, head_dim, block_size, max_pages, chunk_tokens=0) -> int:
+def workspace_bytes(batch, q_heads, kv_heads, head_dim, block_size, max_pages, chunk_tokens=0) -> int:
     """Bytes of scratch ``gqa_decode`` needs for this static shape (worst case over lengths)."""
-    return int(_lib().gqa_b200_workspace_bytes(batch, q_heads, head_dim, block_size, max_pages,
-                                               chunk_tokens))
+    return int(_lib().gqa_b200_workspace_bytes(batch, q_heads, kv_heads, head_dim, block_size,
+                                               max_pages, chunk_tokens))
 
 
 def gqa_decode(q, k_cache, v_cache, block_table, context_lens, *, scale=None, out=None,
@@ -141,8 +141,8 @@ def gqa_decode(q, k_cache, v_cache, block_table, context_lens, *, scale=None, ou
     with torch.cuda.device(q.device):
         stream = _stream_handle(q.device)
         if workspace is None:
-            workspace, need = _workspace_for(lib, q, k_cache.size(1), block_table.size(1),
-                                             chunk_tokens, stream)
+            workspace, need = _workspace_for(lib, q, k_cache.size(2), k_cache.size(1),
+                                             block_table.size(1), chunk_tokens, stream)
         else:
             _check(workspace.is_cuda and workspace.device == q.device and
                    workspace.is_contiguous() and workspace.dtype == torch.uint8,

@@ -63,7 +63,7 @@ struct DecodeParams {
     // planned mode (workspace sections)
     int32_t* hdr;           // kHdrWords int32
     int32_t* chunk_off;     // [batch + 1] exclusive prefix of chunks per sequence
-    int2* items;            // [cap_chunks] (sequence, chunk index)
+    int4* items;            // [cap_chunks] (sequence, partial slot | single<<30, t0, t1)
     float2* part_ml;        // [cap_chunks * q_heads] (max in log2 units, sum)
     float* part_acc;        // [cap_chunks * q_heads * head_dim]
     int cap_chunks;
@@ -109,36 +109,60 @@ __device__ __forceinline__ int total_items(const DecodeParams& p) {
     return p.batch * p.splits * per;
 }
 
+constexpr int kSingleFlag = 1 << 30;   // item record .y: the sequence has one chunk only
+
 // Items are numbered with the kv head fastest, so CTAs that run side by side
-// read neighbouring 2*D-byte rows of the same pages.
-__device__ __forceinline__ WorkItem decode_item(const DecodeParams& p, int item) {
+// read neighbouring 2*D-byte rows of the same pages.  An item's record is
+// (sequence, partial slot or split index [| kSingleFlag], first token, end token): written by the
+// plan kernel in planned mode (one 16-byte load, no dependent reads), computed
+// from context_lens in reference-split mode.
+__device__ __forceinline__ int4 load_item_record(const DecodeParams& p, int item) {
+    const int per = p.kv_heads * p.head_groups;
+    const int cg = item / per;
+    if (p.mode == kModePlanned) return __ldg(p.items + cg);
+    const int b = cg / p.splits;
+    const int z = cg - b * p.splits;
+    const int len = clamp_len(p, b);
+    return make_int4(b, z, (int)(((long long)len * z) / p.splits),
+                     (int)(((long long)len * (z + 1)) / p.splits));
+}
+
+__device__ __forceinline__ WorkItem item_from_record(const DecodeParams& p, int item, int4 rec) {
     WorkItem w;
     const int per = p.kv_heads * p.head_groups;
     const int cg = item / per;
     const int r = item - cg * per;
     w.kvh = r / p.head_groups;
     w.hg = r - w.kvh * p.head_groups;
+    w.b = rec.x;
+    w.part = rec.y & ~kSingleFlag;
+    w.t0 = rec.z;
+    w.t1 = rec.w;
     if (p.mode == kModePlanned) {
-        const int2 bc = __ldg(p.items + cg);
-        w.b = bc.x;
-        w.part = bc.y;
-        const int len = clamp_len(p, w.b);
-        const int ct = chunk_tokens_for(len, p.chunk_base);
-        w.n_parts = chunks_for(len, p.chunk_base);
-        const long long t0 = (long long)w.part * ct;
-        w.t0 = (int)(t0 < len ? t0 : len);
-        w.t1 = (int)(t0 + ct < len ? t0 + ct : len);
-        w.part_slot = cg;
+        w.n_parts = (rec.y & kSingleFlag) ? 1 : 2;   // only "one" vs "several" matters here
+        w.part_slot = w.part;                         // chunk_off[b] + chunk index
     } else {
-        w.b = cg / p.splits;
-        w.part = cg - w.b * p.splits;
-        const int len = clamp_len(p, w.b);
         w.n_parts = p.splits;
-        w.t0 = (int)(((long long)len * w.part) / p.splits);
-        w.t1 = (int)(((long long)len * (w.part + 1)) / p.splits);
         w.part_slot = 0;
     }
     return w;
+}
+
+__device__ __forceinline__ WorkItem decode_item(const DecodeParams& p, int item) {
+    return item_from_record(p, item, load_item_record(p, item));
+}
+
+// Programmatic dependent launch.  Every kernel of this library lets the next
+// kernel in the stream start launching at once and then waits, in every thread
+// and before its first global access, until the kernels before it have
+// completed and flushed.  Because every CTA waits before it can exit, the chain
+// plan -> decode -> merge -> (next call's) plan stays ordered end to end.  When
+// a kernel is launched without the programmatic attribute both are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {

@@ -4,6 +4,7 @@
 #include "../../include/gqa_decode_b200.h"
 
 #include <cmath>
+#include <cstdlib>
 #include <cstdint>
 #include <limits>
 #include <mutex>
@@ -20,6 +21,7 @@ namespace {
 
 constexpr int kTableEntriesBudget = 2048;   // page ids staged in shared memory per segment
 constexpr int kMaxDevices = 64;
+constexpr int kWarpMergeMaxChunks = 16;     // longer sequences use the CTA-per-head merge
 
 struct DeviceInfo {
     int sm_count = 0;
@@ -54,6 +56,7 @@ inline int elem_size(int dtype) { return dtype == GQA_B200_F32 ? 4 : 2; }
 struct WorkspaceLayout {
     size_t hdr, chunk_off, items, part_ml, part_acc, total;
     int cap_chunks;
+    int max_chunks_per_seq;
 };
 
 WorkspaceLayout workspace_layout(int batch, int q_heads, int head_dim, int block_size,
@@ -62,20 +65,40 @@ WorkspaceLayout workspace_layout(int batch, int q_heads, int head_dim, int block
     const long long cap_tokens = (long long)max_pages * block_size;
     const long long per_seq = max_chunks_for_capacity(cap_tokens, chunk_base);
     long long cap = per_seq * (batch > 0 ? batch : 0);
-    if (cap > 0x7fffffffll) cap = 0x7fffffffll;
+    if (cap > 0x3fffffffll) cap = 0x3fffffffll;   // bit 30 of a slot is the single-chunk flag
     w.cap_chunks = (int)cap;
+    w.max_chunks_per_seq = (int)(per_seq > 0x7fffffffll ? 0x7fffffffll : per_seq);
     size_t at = 0;
     w.hdr = at;        at = align_up(at + kHdrWords * sizeof(int32_t), 256);
     w.chunk_off = at;  at = align_up(at + ((size_t)batch + 1) * sizeof(int32_t), 256);
-    w.items = at;      at = align_up(at + (size_t)cap * sizeof(int2), 256);
+    w.items = at;      at = align_up(at + (size_t)cap * sizeof(int4), 256);
     w.part_ml = at;    at = align_up(at + (size_t)cap * q_heads * sizeof(float2), 256);
     w.part_acc = at;   at = align_up(at + (size_t)cap * q_heads * head_dim * sizeof(float), 256);
     w.total = at;
     return w;
 }
 
-int resolve_chunk_base(int chunk_tokens) {
-    if (chunk_tokens == 0) return kDefaultChunkTokens;
+// chunk_tokens == 0: pick the base chunk length from the static shape alone (no
+// read of context_lens): the largest of 1024 .. 64 that still cuts a full table
+// into at least kItemsPerSlot items per resident CTA, so small batches are split
+// finely enough to fill the GPU and large ones pay little per-item overhead.
+constexpr int kAssumedCtaSlots = 2 * 148;   // B200: 148 SMs x 2 resident decode CTAs
+constexpr int kItemsPerSlot = 4;
+
+int auto_chunk_base(int batch, int q_heads, int kv_heads, int block_size, int max_pages) {
+    const long long cap_tokens = (long long)max_pages * block_size;
+    const int group = q_heads / kv_heads;
+    const long long per_chunk = (long long)batch * kv_heads * ((group + 15) / 16);
+    for (int base = 1024; base > 64; base >>= 1) {
+        const long long chunks = (cap_tokens + base - 1) / base;
+        if (per_chunk * chunks >= (long long)kItemsPerSlot * kAssumedCtaSlots) return base;
+    }
+    return 64;
+}
+
+int resolve_chunk_base(int chunk_tokens, int batch, int q_heads, int kv_heads, int block_size,
+                       int max_pages) {
+    if (chunk_tokens == 0) return auto_chunk_base(batch, q_heads, kv_heads, block_size, max_pages);
     if (chunk_tokens < kMinChunkTokens || chunk_tokens > kMaxChunkTokens) return -1;
     return chunk_tokens;
 }
@@ -183,6 +206,34 @@ cudaError_t resident_ctas(KernelT kernel, int threads, size_t smem, int smem_lim
     return cudaSuccess;
 }
 
+// Launch with the programmatic-stream-serialization attribute, so the kernel may
+// begin launching while the kernel before it in the stream drains (each kernel
+// waits on-device before touching memory; see pdl_wait).  GQA_B200_NO_PDL=1 in the
+// environment falls back to plain stream order.
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("GQA_B200_NO_PDL");
+        return !(v && v[0] == '1');
+    }();
+    return on;
+}
+
+template <typename KernelT>
+cudaError_t launch_kernel(KernelT kernel, dim3 grid, int threads, size_t smem, cudaStream_t stream,
+                          const DecodeParams& p) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 template <typename KernelT>
 cudaError_t launch_persistent(KernelT kernel, const DecodeParams& p, int threads, size_t smem,
                               int max_ctas, long long item_bound, cudaStream_t stream) {
@@ -198,14 +249,12 @@ cudaError_t launch_persistent(KernelT kernel, const DecodeParams& p, int threads
     if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
     if (grid > item_bound) grid = item_bound;
     if (grid < 1) grid = 1;
-    kernel<<<(unsigned)grid, threads, smem, stream>>>(p);
-    return cudaGetLastError();
+    return launch_kernel(kernel, dim3((unsigned)grid), threads, smem, stream, p);
 }
 
-template <typename T, int D, int TILE_N, int NSTAGES, int MIN_CTAS>
+template <typename T, int D, int TILE_N, int NSTAGES, int MIN_CTAS, int NWARPS = 4>
 cudaError_t launch_mma(const DecodeParams& p, int max_ctas, long long item_bound,
                        cudaStream_t stream) {
-    constexpr int NWARPS = 4;
     using G = MmaGeom<D, TILE_N, NSTAGES, NWARPS>;
     const size_t smem = G::kFixedBytes + (size_t)p.table_smem_entries * sizeof(int);
     return launch_persistent(gqa_decode_mma_kernel<T, D, TILE_N, NSTAGES, NWARPS, MIN_CTAS>, p,
@@ -217,7 +266,19 @@ cudaError_t launch_mma_for_dim(const DecodeParams& p, int max_ctas, long long it
                                cudaStream_t stream) {
     switch (p.head_dim) {
         case 64:  return launch_mma<T, 64, 32, 3, 2>(p, max_ctas, item_bound, stream);
-        case 128: return launch_mma<T, 128, 16, 3, 2>(p, max_ctas, item_bound, stream);
+        case 128:
+#ifdef GQA_B200_TUNING
+            switch (getenv("GQA_B200_VARIANT") ? atoi(getenv("GQA_B200_VARIANT")) : 0) {
+                case 1: return launch_mma<T, 128, 16, 2, 3>(p, max_ctas, item_bound, stream);
+                case 2: return launch_mma<T, 128, 16, 3, 1, 8>(p, max_ctas, item_bound, stream);
+                case 3: return launch_mma<T, 128, 16, 2, 2, 6>(p, max_ctas, item_bound, stream);
+                case 4: return launch_mma<T, 128, 16, 4, 1, 6>(p, max_ctas, item_bound, stream);
+                case 5: return launch_mma<T, 128, 16, 2, 2>(p, max_ctas, item_bound, stream);
+                case 6: return launch_mma<T, 128, 32, 3, 1>(p, max_ctas, item_bound, stream);
+                default: break;
+            }
+#endif
+            return launch_mma<T, 128, 16, 3, 2>(p, max_ctas, item_bound, stream);
         case 256: return launch_mma<T, 256, 16, 3, 1>(p, max_ctas, item_bound, stream);
         default:  return cudaErrorInvalidValue;
     }
@@ -304,19 +365,24 @@ cudaError_t launch_decode(DecodeParams& p, int dtype, bool use_mma, int max_ctas
 }
 
 template <typename T>
-cudaError_t launch_merge_t(const DecodeParams& p, cudaStream_t stream) {
-    const dim3 grid((unsigned)p.q_heads, (unsigned)p.batch);
+cudaError_t launch_merge_t(const DecodeParams& p, int max_chunks_per_seq, cudaStream_t stream) {
     const bool vec4 = p.mode == kModePlanned && p.head_dim % 4 == 0;
-    if (vec4) gqa_merge_kernel<T, true><<<grid, kMergeWarps * 32, 0, stream>>>(p);
-    else gqa_merge_kernel<T, false><<<grid, kMergeWarps * 32, 0, stream>>>(p);
-    return cudaGetLastError();
+    if (vec4 && max_chunks_per_seq <= kWarpMergeMaxChunks) {
+        const long long pairs = (long long)p.batch * p.q_heads;
+        const unsigned grid = (unsigned)((pairs + kMergeWarps - 1) / kMergeWarps);
+        return launch_kernel(gqa_merge_warp_kernel<T>, dim3(grid), kMergeWarps * 32, 0, stream, p);
+    }
+    const dim3 grid((unsigned)p.q_heads, (unsigned)p.batch);
+    if (vec4) return launch_kernel(gqa_merge_kernel<T, true>, grid, kMergeWarps * 32, 0, stream, p);
+    return launch_kernel(gqa_merge_kernel<T, false>, grid, kMergeWarps * 32, 0, stream, p);
 }
 
-cudaError_t launch_merge(const DecodeParams& p, int dtype, cudaStream_t stream) {
+cudaError_t launch_merge(const DecodeParams& p, int dtype, int max_chunks_per_seq,
+                         cudaStream_t stream) {
     switch (dtype) {
-        case GQA_B200_F32:  return launch_merge_t<float>(p, stream);
-        case GQA_B200_F16:  return launch_merge_t<__half>(p, stream);
-        default:            return launch_merge_t<__nv_bfloat16>(p, stream);
+        case GQA_B200_F32:  return launch_merge_t<float>(p, max_chunks_per_seq, stream);
+        case GQA_B200_F16:  return launch_merge_t<__half>(p, max_chunks_per_seq, stream);
+        default:            return launch_merge_t<__nv_bfloat16>(p, max_chunks_per_seq, stream);
     }
 }
 
@@ -351,24 +417,32 @@ const char* gqa_b200_strerror(int code) {
     return "unknown gqa_b200 status";
 }
 
+int gqa_b200_auto_chunk_tokens(int batch, int q_heads, int kv_heads, int block_size,
+                               int max_pages) {
+    if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads || block_size <= 0 ||
+        max_pages <= 0)
+        return GQA_B200_ERR_HEADS;
+    return auto_chunk_base(batch, q_heads, kv_heads, block_size, max_pages);
+}
+
 int gqa_b200_chunk_tokens(int context_len, int chunk_tokens) {
-    const int base = resolve_chunk_base(chunk_tokens);
-    if (base < 0) return GQA_B200_ERR_CHUNK;
-    return chunk_tokens_for(context_len < 0 ? 0 : context_len, base);
+    if (chunk_tokens < kMinChunkTokens || chunk_tokens > kMaxChunkTokens) return GQA_B200_ERR_CHUNK;
+    return chunk_tokens_for(context_len < 0 ? 0 : context_len, chunk_tokens);
 }
 
 int gqa_b200_max_chunks_per_seq(int max_pages, int block_size, int chunk_tokens) {
-    const int base = resolve_chunk_base(chunk_tokens);
-    if (base < 0) return GQA_B200_ERR_CHUNK;
+    if (chunk_tokens < kMinChunkTokens || chunk_tokens > kMaxChunkTokens) return GQA_B200_ERR_CHUNK;
     if (max_pages <= 0 || block_size <= 0) return 0;
-    return max_chunks_for_capacity((long long)max_pages * block_size, base);
+    return max_chunks_for_capacity((long long)max_pages * block_size, chunk_tokens);
 }
 
-size_t gqa_b200_workspace_bytes(int batch, int q_heads, int head_dim, int block_size,
+size_t gqa_b200_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim, int block_size,
                                 int max_pages, int chunk_tokens) {
-    const int base = resolve_chunk_base(chunk_tokens);
-    if (base < 0 || batch < 0 || q_heads <= 0 || head_dim <= 0 || block_size <= 0 || max_pages <= 0)
+    if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads || head_dim <= 0 ||
+        block_size <= 0 || max_pages <= 0)
         return 0;
+    const int base = resolve_chunk_base(chunk_tokens, batch, q_heads, kv_heads, block_size, max_pages);
+    if (base < 0) return 0;
     return workspace_layout(batch, q_heads, head_dim, block_size, max_pages, base).total;
 }
 
@@ -381,7 +455,7 @@ int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
     int rc = check_common(q, k_cache, v_cache, block_table, context_lens, out, dtype, batch,
                           q_heads, kv_heads, head_dim, num_blocks, block_size, max_pages, scale);
     if (rc != GQA_B200_OK) return rc;
-    const int base = resolve_chunk_base(chunk_tokens);
+    const int base = resolve_chunk_base(chunk_tokens, batch, q_heads, kv_heads, block_size, max_pages);
     if (base < 0) return GQA_B200_ERR_CHUNK;
     if (kernel != GQA_B200_KERNEL_AUTO && kernel != GQA_B200_KERNEL_SIMT &&
         kernel != GQA_B200_KERNEL_MMA)
@@ -398,7 +472,7 @@ int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
     char* ws = static_cast<char*>(workspace);
     p.hdr = reinterpret_cast<int32_t*>(ws + lay.hdr);
     p.chunk_off = reinterpret_cast<int32_t*>(ws + lay.chunk_off);
-    p.items = reinterpret_cast<int2*>(ws + lay.items);
+    p.items = reinterpret_cast<int4*>(ws + lay.items);
     p.part_ml = reinterpret_cast<float2*>(ws + lay.part_ml);
     p.part_acc = reinterpret_cast<float*>(ws + lay.part_acc);
     p.cap_chunks = lay.cap_chunks;
@@ -415,15 +489,14 @@ int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
     if (phases == 0) phases = GQA_B200_PHASE_PLAN | GQA_B200_PHASE_DECODE | GQA_B200_PHASE_MERGE;
     cudaError_t e = cudaSuccess;
     if (phases & GQA_B200_PHASE_PLAN) {
-        gqa_plan_kernel<<<1, kPlanThreads, 0, s>>>(p);
-        e = cudaGetLastError();
+        e = launch_kernel(gqa_plan_kernel, dim3(1), kPlanThreads, 0, s, p);
         if (e != cudaSuccess) return (int)e;
     }
     if (phases & GQA_B200_PHASE_DECODE) {
         e = launch_decode(p, dtype, use_mma, max_ctas, s);
         if (e != cudaSuccess) return (int)e;
     }
-    if (phases & GQA_B200_PHASE_MERGE) e = launch_merge(p, dtype, s);
+    if (phases & GQA_B200_PHASE_MERGE) e = launch_merge(p, dtype, lay.max_chunks_per_seq, s);
     return (int)e;
 }
 
@@ -463,7 +536,7 @@ int gqa_b200_decode_split(const void* q, const void* k_cache, const void* v_cach
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e = launch_decode(p, dtype, use_mma, 0, s);
     if (e != cudaSuccess) return (int)e;
-    if (splits > 1) e = launch_merge(p, dtype, s);
+    if (splits > 1) e = launch_merge(p, dtype, splits, s);
     return (int)e;
 }
 

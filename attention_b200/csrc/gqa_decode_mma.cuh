@@ -94,6 +94,14 @@ template <int D, int TILE_N, int NSTAGES, int NWARPS> struct MmaGeom {
     static_assert(TILE_N % 16 == 0, "tile is a multiple of the mma K step");
 };
 
+// Lazy rescaling: the running maximum used as the exponent reference is only
+// moved when a tile's maximum exceeds it by more than kRescaleSlack (log2
+// units), so the O accumulators are rescaled a few times per item instead of
+// once per tile.  Probabilities then lie in (0, 2^kRescaleSlack], exact in
+// fp32 and well inside fp16/bf16 range; (m, l, O) stay mutually consistent, so
+// the normalised result is unchanged.
+constexpr float kRescaleSlack = 8.f;
+
 template <typename T, int D, int TILE_N, int NSTAGES, int NWARPS, int MIN_CTAS>
 __global__ void __launch_bounds__(NWARPS * 32, MIN_CTAS)
 gqa_decode_mma_kernel(const DecodeParams p) {
@@ -103,6 +111,7 @@ gqa_decode_mma_kernel(const DecodeParams p) {
     constexpr int CPR = G::kChunksPerRow;
     constexpr int ROWS_PER_IT = 32 / CPR;
     constexpr int LD_ITERS = TILE_N / ROWS_PER_IT;
+    constexpr int SUB_ITERS = 16 / ROWS_PER_IT;   // copy passes per 16-token sub-tile
     constexpr int NB = TILE_N / 8;    // n-blocks of S
     constexpr int KS = D / 16;        // k-steps of Q.K^T
     constexpr int ND = D / 8;         // n-blocks of O
@@ -128,11 +137,20 @@ gqa_decode_mma_kernel(const DecodeParams p) {
     const char* vc = reinterpret_cast<const char*>(p.v);
     const T* qp = reinterpret_cast<const T*>(p.q);
     const long long row_bytes_all = (long long)p.kv_heads * ROWB;   // one token, all kv heads
+    pdl_launch_dependents();
+    pdl_wait();   // the plan kernel wrote hdr / items
     const int n_items = total_items(p);
 
-    // per-lane constants of the tile copy: row within a pass, 16-byte chunk, swizzled offset
+    // per-lane constants of the tile copy: row within a pass and 16-byte chunk
     const int ld_row = lane / CPR;
     const int ld_cc = lane % CPR;
+    // per-lane constants of the ldmatrix addresses (swizzle: chunk ^ (row & 7))
+    const uint32_t k_lane_off = (lane & 7) * ROWB;                    // K: token row within an n-block
+    const uint32_t k_lane_x = (lane >> 3) ^ (lane & 7);               // chunk 4kp + (lane>>3)
+    const uint32_t v_lane_off = (((lane >> 3) & 1) * 8 + (lane & 7)) * ROWB;   // V: token row in a k-step
+    const uint32_t v_lane_x = (lane >> 4) ^ (lane & 7);               // chunk 2np + (lane>>4)
+    // 16-token sub-tiles sit inside one page when the page size is a power of two >= 16
+    const bool pages_hold_subtiles = p.bs_shift >= 4;
 
     int item;
     if (p.mode == kModePlanned) {
@@ -142,6 +160,8 @@ gqa_decode_mma_kernel(const DecodeParams p) {
     } else {
         item = blockIdx.x;
     }
+    int4 rec = make_int4(0, 0, 0, 0);
+    if (item < n_items) rec = load_item_record(p, item);
 
     while (item < n_items) {
         int next = 0;
@@ -150,12 +170,11 @@ gqa_decode_mma_kernel(const DecodeParams p) {
         } else {
             next = item + gridDim.x;
         }
-        const WorkItem w = decode_item(p, item);
+        const WorkItem w = item_from_record(p, item, rec);
         const int rows_valid = min(16, p.group - w.hg * 16);
+        const bool nonempty = w.t1 > w.t0;
 
-        if (w.t1 <= w.t0) {
-            store_empty<T>(p, w, rows_valid);
-        } else {
+        if (nonempty) {
             // ---- Q fragments (A operand: rows = query heads, padded with zeros) ----
             uint32_t qa[QREGS][4];
             const int head0 = w.kvh * p.group + w.hg * 16;
@@ -172,7 +191,6 @@ gqa_decode_mma_kernel(const DecodeParams p) {
                     qa[ks][3] = v1 ? __ldg(reinterpret_cast<const uint32_t*>(q1 + c + 8)) : 0u;
                 }
             } else {
-                __syncthreads();   // previous item's Q no longer read
                 for (int i = tid; i < 16 * CPR; i += NWARPS * 32) {
                     const int row = i / CPR, cc = i % CPR;
                     uint4 val = make_uint4(0u, 0u, 0u, 0u);
@@ -191,12 +209,13 @@ gqa_decode_mma_kernel(const DecodeParams p) {
             for (int s0 = w.t0; s0 < w.t1; s0 += p.seg_tokens) {
                 const int s1 = min(w.t1, s0 + p.seg_tokens);
                 int first_page;
-                __syncthreads();   // previous segment's table (and all rings) idle
+                if (s0 != w.t0) __syncthreads();   // previous segment's table no longer read
                 stage_table(p, w.b, s0, s1, s_table, first_page);
                 __syncthreads();
 
                 const int n_tiles = (s1 - s0 + TILE_N - 1) / TILE_N;
                 const int my_tiles = n_tiles > warp ? (n_tiles - warp + NWARPS - 1) / NWARPS : 0;
+                const bool fast_segment = pages_hold_subtiles && (s0 & 15) == 0;
 
                 // issue the copies of this warp's k-th tile (and always commit a group)
                 auto issue = [&](int k) {
@@ -204,22 +223,46 @@ gqa_decode_mma_kernel(const DecodeParams p) {
                         const int tile_t0 = s0 + (warp + k * NWARPS) * TILE_N;
                         const uint32_t sk = ring_u32 + (k % NSTAGES) * G::kStageBytes;
                         const uint32_t sv = sk + G::kTileBytes;
+                        if (fast_segment && tile_t0 + TILE_N <= s1) {
+                            // whole tile valid, each 16-token sub-tile inside one page: one
+                            // table lookup per sub-tile, then a constant source stride
 #pragma unroll
-                        for (int it = 0; it < LD_ITERS; ++it) {
-                            const int row = it * ROWS_PER_IT + ld_row;
-                            const int t = tile_t0 + row;
-                            const bool valid = t < s1;
-                            long long off = 0;
-                            if (valid) {
-                                int pg, slot;
-                                token_page_slot(p, t, pg, slot);
-                                const long long phys = s_table[pg - first_page];
-                                off = (phys * p.block_size + slot) * row_bytes_all +
-                                      (long long)w.kvh * ROWB + ld_cc * 16;
+                            for (int sub = 0; sub < TILE_N / 16; ++sub) {
+                                const int t = tile_t0 + sub * 16;
+                                const long long phys = s_table[(t >> p.bs_shift) - first_page];
+                                const int slot = (t & (p.block_size - 1)) + ld_row;
+                                const long long off = (phys * p.block_size + slot) * row_bytes_all +
+                                                      (long long)w.kvh * ROWB + ld_cc * 16;
+                                const char* ks = kc + off;
+                                const char* vs = vc + off;
+#pragma unroll
+                                for (int it = 0; it < SUB_ITERS; ++it) {
+                                    const int row = sub * 16 + it * ROWS_PER_IT + ld_row;
+                                    const uint32_t dst = row * ROWB + ((ld_cc ^ (row & 7)) << 4);
+                                    cp_async16(sk + dst, ks, 16);
+                                    cp_async16(sv + dst, vs, 16);
+                                    ks += ROWS_PER_IT * row_bytes_all;
+                                    vs += ROWS_PER_IT * row_bytes_all;
+                                }
                             }
-                            const uint32_t dst = row * ROWB + ((ld_cc ^ (row & 7)) << 4);
-                            cp_async16(sk + dst, kc + off, valid ? 16 : 0);
-                            cp_async16(sv + dst, vc + off, valid ? 16 : 0);
+                        } else {
+#pragma unroll 1
+                            for (int it = 0; it < LD_ITERS; ++it) {
+                                const int row = it * ROWS_PER_IT + ld_row;
+                                const int t = tile_t0 + row;
+                                const bool valid = t < s1;
+                                long long off = 0;
+                                if (valid) {
+                                    int pg, slot;
+                                    token_page_slot(p, t, pg, slot);
+                                    const long long phys = s_table[pg - first_page];
+                                    off = (phys * p.block_size + slot) * row_bytes_all +
+                                          (long long)w.kvh * ROWB + ld_cc * 16;
+                                }
+                                const uint32_t dst = row * ROWB + ((ld_cc ^ (row & 7)) << 4);
+                                cp_async16(sk + dst, kc + off, valid ? 16 : 0);
+                                cp_async16(sv + dst, vc + off, valid ? 16 : 0);
+                            }
                         }
                     }
                     cp_async_commit();
@@ -261,10 +304,9 @@ gqa_decode_mma_kernel(const DecodeParams p) {
 #pragma unroll
                         for (int nb = 0; nb < NB; ++nb) {
                             // matrices: (tokens nb*8..+7) x 16-byte chunks 4kp .. 4kp+3
-                            const int row = nb * 8 + (lane & 7);
-                            const int cc = 4 * kp + (lane >> 3);
                             uint32_t b0, b1, b2, b3;
-                            ldmatrix_x4(sk + row * ROWB + ((cc ^ (row & 7)) << 4), b0, b1, b2, b3);
+                            ldmatrix_x4(sk + nb * 8 * ROWB + k_lane_off + ((k_lane_x ^ (4 * kp)) << 4),
+                                        b0, b1, b2, b3);
                             Ops::mma(s[nb], a0, b0, b1);
                             Ops::mma(s[nb], a1, b2, b3);
                         }
@@ -289,33 +331,33 @@ gqa_decode_mma_kernel(const DecodeParams p) {
                     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
                     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
                     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-                    // the first token of a tile is always valid, so the new max is finite
-                    const float mn0 = fmaxf(m0, mx0 * p.scale_log2);
-                    const float mn1 = fmaxf(m1, mx1 * p.scale_log2);
-                    const float alpha0 = fast_exp2(m0 - mn0), alpha1 = fast_exp2(m1 - mn1);
-                    m0 = mn0;
-                    m1 = mn1;
-                    float ps0 = 0.f, ps1 = 0.f;
-                    uint32_t pa[KK][4];
-#pragma unroll
-                    for (int nb = 0; nb < NB; ++nb) {
-                        const float p0 = fast_exp2(fmaf(s[nb][0], p.scale_log2, -mn0));
-                        const float p1 = fast_exp2(fmaf(s[nb][1], p.scale_log2, -mn0));
-                        const float p2 = fast_exp2(fmaf(s[nb][2], p.scale_log2, -mn1));
-                        const float p3 = fast_exp2(fmaf(s[nb][3], p.scale_log2, -mn1));
-                        ps0 += p0 + p1;
-                        ps1 += p2 + p3;
-                        pa[nb >> 1][(nb & 1) * 2 + 0] = Ops::pack(p0, p1);
-                        pa[nb >> 1][(nb & 1) * 2 + 1] = Ops::pack(p2, p3);
-                    }
-                    l0 = l0 * alpha0 + ps0;
-                    l1 = l1 * alpha1 + ps1;
-                    if (__any_sync(0xffffffffu, alpha0 != 1.f || alpha1 != 1.f)) {
+                    // the first token of a tile is always valid, so the tile maxima are finite
+                    mx0 *= p.scale_log2;
+                    mx1 *= p.scale_log2;
+                    if (__any_sync(0xffffffffu, mx0 > m0 + kRescaleSlack || mx1 > m1 + kRescaleSlack)) {
+                        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+                        const float alpha0 = fast_exp2(m0 - mn0), alpha1 = fast_exp2(m1 - mn1);
+                        m0 = mn0;
+                        m1 = mn1;
+                        l0 *= alpha0;
+                        l1 *= alpha1;
 #pragma unroll
                         for (int nd = 0; nd < ND; ++nd) {
                             o[nd][0] *= alpha0; o[nd][1] *= alpha0;
                             o[nd][2] *= alpha1; o[nd][3] *= alpha1;
                         }
+                    }
+                    uint32_t pa[KK][4];
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb) {
+                        const float p0 = fast_exp2(fmaf(s[nb][0], p.scale_log2, -m0));
+                        const float p1 = fast_exp2(fmaf(s[nb][1], p.scale_log2, -m0));
+                        const float p2 = fast_exp2(fmaf(s[nb][2], p.scale_log2, -m1));
+                        const float p3 = fast_exp2(fmaf(s[nb][3], p.scale_log2, -m1));
+                        l0 += p0 + p1;
+                        l1 += p2 + p3;
+                        pa[nb >> 1][(nb & 1) * 2 + 0] = Ops::pack(p0, p1);
+                        pa[nb >> 1][(nb & 1) * 2 + 1] = Ops::pack(p2, p3);
                     }
 
                     // ---- O += P V : [16 heads] x [D] ----
@@ -324,11 +366,10 @@ gqa_decode_mma_kernel(const DecodeParams p) {
 #pragma unroll
                         for (int np = 0; np < ND / 2; ++np) {
                             // matrices: tokens kk*16 + {0..7, 8..15} x chunks 2np, 2np+1
-                            const int row = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
-                            const int cc = 2 * np + (lane >> 4);
                             uint32_t b0, b1, b2, b3;
-                            ldmatrix_x4_trans(sv + row * ROWB + ((cc ^ (row & 7)) << 4), b0, b1, b2,
-                                              b3);
+                            ldmatrix_x4_trans(sv + kk * 16 * ROWB + v_lane_off +
+                                                  ((v_lane_x ^ (2 * np)) << 4),
+                                              b0, b1, b2, b3);
                             Ops::mma(o[2 * np], pa[kk], b0, b1);
                             Ops::mma(o[2 * np + 1], pa[kk], b2, b3);
                         }
@@ -337,7 +378,7 @@ gqa_decode_mma_kernel(const DecodeParams p) {
                 cp_async_wait<0>();
             }
 
-            // ---- publish this warp's state, then combine across warps ----
+            // ---- publish this warp's state ----
             l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
             l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
             l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
@@ -357,19 +398,23 @@ gqa_decode_mma_kernel(const DecodeParams p) {
                 s_l[warp * 16 + r0] = l0;
                 s_l[warp * 16 + r0 + 8] = l1;
             }
-            __syncthreads();
+        }
+        if (tid == 0) s_item = next;
+        __syncthreads();
+        // fetch the next item's record now; its latency hides behind the combine
+        const int nxt = s_item;
+        int4 rec_next = make_int4(0, 0, 0, 0);
+        if (nxt < n_items) rec_next = load_item_record(p, nxt);
+        if (nonempty) {
             combine_and_store<T, NWARPS, true>(p, w, reinterpret_cast<const float*>(s_ring),
                                                G::kWarpBytes / 4, G::kOStride, s_m, s_l, 16,
                                                rows_valid);
-        }
-        __syncthreads();
-        if (p.mode == kModePlanned) {
-            if (tid == 0) s_item = next;
-            __syncthreads();
-            item = s_item;
         } else {
-            item = next;
+            store_empty<T>(p, w, rows_valid);
         }
+        __syncthreads();   // rings, Q tile, table and s_item are free again
+        item = nxt;
+        rec = rec_next;
     }
 }
 

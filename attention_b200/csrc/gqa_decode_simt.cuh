@@ -69,6 +69,8 @@ gqa_decode_simt_kernel(const DecodeParams p) {
     const T* kc = reinterpret_cast<const T*>(p.k);
     const T* vc = reinterpret_cast<const T*>(p.v);
     const T* qp = reinterpret_cast<const T*>(p.q);
+    pdl_launch_dependents();
+    pdl_wait();   // the plan kernel wrote hdr / items
     const int n_items = total_items(p);
     const long long row_elems = (long long)p.kv_heads * D;
 

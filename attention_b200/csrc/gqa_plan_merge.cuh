@@ -8,53 +8,70 @@ namespace gqa_b200 {
 
 constexpr int kPlanThreads = 1024;
 
-// One CTA.  Reads context_lens, writes the exclusive prefix of chunks per
-// sequence, the (sequence, chunk) item list, the total, and zeroes the decode
-// kernel's work counter.  No host read of the lengths is ever needed.
-__global__ void __launch_bounds__(kPlanThreads) gqa_plan_kernel(const DecodeParams p) {
-    __shared__ int s_warp[kPlanThreads / 32];
-    __shared__ int s_running;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid == 0) s_running = 0;
+// Block-wide inclusive scan of one int per thread (kPlanThreads threads).
+__device__ __forceinline__ int plan_block_scan(int x, int* s_warp, int& total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, x, d);
+        if (lane >= d) x += y;
+    }
+    __syncthreads();                 // s_warp free from the previous use
+    if (lane == 31) s_warp[warp] = x;
     __syncthreads();
-    for (int base = 0; base < p.batch; base += kPlanThreads) {
-        const int b = base + tid;
-        const int n = b < p.batch ? chunks_for(clamp_len(p, b), p.chunk_base) : 0;
-        int incl = n;
+    if (warp == 0) {
+        int t = s_warp[lane];
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
-            const int y = __shfl_up_sync(0xffffffffu, incl, d);
-            if (lane >= d) incl += y;
+            const int y = __shfl_up_sync(0xffffffffu, t, d);
+            if (lane >= d) t += y;
         }
-        if (lane == 31) s_warp[warp] = incl;
-        __syncthreads();
-        if (warp == 0) {
-            int x = s_warp[lane];
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const int y = __shfl_up_sync(0xffffffffu, x, d);
-                if (lane >= d) x += y;
-            }
-            s_warp[lane] = x;   // inclusive prefix of warp totals
-        }
-        __syncthreads();
-        const int running = s_running;
-        const int off = running + (warp ? s_warp[warp - 1] : 0) + incl - n;
+        s_warp[lane] = t;
+    }
+    __syncthreads();
+    total = s_warp[kPlanThreads / 32 - 1];
+    return x + (warp ? s_warp[warp - 1] : 0);
+}
+
+// One CTA.  Reads context_lens and writes, without any host read of the lengths:
+//   chunk_off[b]  exclusive prefix of chunks per sequence (the partial slots of
+//                 sequence b are chunk_off[b] .. chunk_off[b+1]-1)
+//   items[]       one record per chunk, in sequence order.  (Putting all short
+//                 last chunks at the end of the list was measured slower: equal
+//                 items make every CTA start and drain its copy pipeline at the
+//                 same moments.)
+//   hdr           chunk total, status, and the zeroed work counter
+__global__ void __launch_bounds__(kPlanThreads) gqa_plan_kernel(const DecodeParams p) {
+    __shared__ int s_warp[kPlanThreads / 32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x;
+    int run_n = 0;
+    for (int base = 0; base < p.batch; base += kPlanThreads) {
+        const int b = base + tid;
+        const int len = b < p.batch ? clamp_len(p, b) : 0;
+        const int n = chunks_for(len, p.chunk_base);
+        int tot_n;
+        const int incl_n = plan_block_scan(n, s_warp, tot_n);
         if (b < p.batch) {
-            p.chunk_off[b] = off;
-            for (int c = 0; c < n; ++c)
-                if (off + c < p.cap_chunks) p.items[off + c] = make_int2(b, c);
+            const int co = run_n + incl_n - n;
+            p.chunk_off[b] = co;
+            const int ct = chunk_tokens_for(len, p.chunk_base);
+            const int flag = n == 1 ? kSingleFlag : 0;
+            for (int c = 0; c < n; ++c) {
+                const long long t0 = (long long)c * ct;
+                const int t1 = (int)(t0 + ct < len ? t0 + ct : len);
+                if (co + c < p.cap_chunks)
+                    p.items[co + c] = make_int4(b, (co + c) | flag, (int)t0, t1);
+            }
         }
-        __syncthreads();
-        if (tid == 0) s_running = running + s_warp[kPlanThreads / 32 - 1];
-        __syncthreads();
+        run_n += tot_n;
     }
     if (tid == 0) {
-        const int total = s_running;
-        p.chunk_off[p.batch] = total;
-        p.hdr[kHdrTotalChunks] = total;
+        p.chunk_off[p.batch] = run_n;
+        p.hdr[kHdrTotalChunks] = run_n;
         p.hdr[kHdrCounter] = 0;
-        p.hdr[kHdrStatus] = total > p.cap_chunks ? 1 : 0;
+        p.hdr[kHdrStatus] = run_n > p.cap_chunks ? 1 : 0;
     }
 }
 
@@ -70,6 +87,8 @@ constexpr int kMergeWarps = 4;
 // [B, Hq, S, D+2] buffer with max in natural units.
 template <typename T, bool VEC4>
 __global__ void __launch_bounds__(kMergeWarps * 32) gqa_merge_kernel(const DecodeParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int hq = blockIdx.x, b = blockIdx.y;
     const int D = p.head_dim;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -168,6 +187,69 @@ __global__ void __launch_bounds__(kMergeWarps * 32) gqa_merge_kernel(const Decod
         for (int wp = 0; wp < kMergeWarps; ++wp) x += s_acc[wp][col];
         out[col] = from_f32<T>(x * inv);
     }
+}
+
+// Planned-mode merge for short sequences (few chunks each): one WARP per
+// (sequence, query head), four pairs per CTA; lanes own float4 columns and the
+// chunk loop is unrolled so several partial rows are in flight.  head_dim % 4 == 0.
+template <typename T>
+__global__ void __launch_bounds__(kMergeWarps * 32) gqa_merge_warp_kernel(const DecodeParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long pair = (long long)blockIdx.x * kMergeWarps + warp;
+    if (pair >= (long long)p.batch * p.q_heads) return;
+    const int b = (int)(pair / p.q_heads), hq = (int)(pair - (long long)b * p.q_heads);
+    const int D = p.head_dim;
+    const int c0 = p.chunk_off[b];
+    int n = p.chunk_off[b + 1] - c0;
+    if (c0 + n > p.cap_chunks) n = p.cap_chunks > c0 ? p.cap_chunks - c0 : 0;
+    if (n == 1) return;
+    T* out = reinterpret_cast<T*>(p.out) + ((size_t)b * p.q_heads + hq) * D;
+    const int col0 = lane * 4, col1 = (32 + lane) * 4;
+    auto store4 = [&](int col, float x0, float x1, float x2, float x3) {
+        if (sizeof(T) == 4) {
+            *reinterpret_cast<float4*>(out + col) = make_float4(x0, x1, x2, x3);
+        } else {
+            T tmp[4] = {from_f32<T>(x0), from_f32<T>(x1), from_f32<T>(x2), from_f32<T>(x3)};
+            *reinterpret_cast<uint2*>(out + col) = *reinterpret_cast<const uint2*>(tmp);
+        }
+    };
+    if (n == 0) {
+        if (col0 < D) store4(col0, 0.f, 0.f, 0.f, 0.f);
+        if (col1 < D) store4(col1, 0.f, 0.f, 0.f, 0.f);
+        return;
+    }
+    const float2* ml = p.part_ml + (size_t)c0 * p.q_heads + hq;
+    const float* acc = p.part_acc + ((size_t)c0 * p.q_heads + hq) * D;
+    const size_t ml_step = p.q_heads, acc_step = (size_t)p.q_heads * D;
+    float mx = -INFINITY;
+    for (int c = lane; c < n; c += 32) {
+        const float2 v = ml[c * ml_step];
+        if (v.y > 0.f) mx = fmaxf(mx, v.x);
+    }
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+    float sum = 0.f;
+#pragma unroll 4
+    for (int c = 0; c < n; ++c) {
+        const float2 v = ml[c * ml_step];
+        const float wgt = v.y > 0.f ? fast_exp2(v.x - mx) : 0.f;
+        sum += wgt * v.y;
+        const float* src = acc + c * acc_step;
+        if (col0 < D) {
+            const float4 x = *reinterpret_cast<const float4*>(src + col0);
+            a0.x += wgt * x.x; a0.y += wgt * x.y; a0.z += wgt * x.z; a0.w += wgt * x.w;
+        }
+        if (col1 < D) {
+            const float4 x = *reinterpret_cast<const float4*>(src + col1);
+            a1.x += wgt * x.x; a1.y += wgt * x.y; a1.z += wgt * x.z; a1.w += wgt * x.w;
+        }
+    }
+    const float inv = sum > 0.f ? 1.f / sum : 0.f;
+    if (col0 < D) store4(col0, a0.x * inv, a0.y * inv, a0.z * inv, a0.w * inv);
+    if (col1 < D) store4(col1, a1.x * inv, a1.y * inv, a1.z * inv, a1.w * inv);
 }
 
 }  // namespace gqa_b200

@@ -281,7 +281,7 @@ def run_b200(args):
     ms_total = ev0.elapsed_time(ev1)
 
     # ---- roofline: the decode kernel alone, its own events on the launching stream ----
-    ws = torch.empty(attn.workspace_bytes(w.batch, w.q_heads, w.head_dim, w.block_size,
+    ws = torch.empty(attn.workspace_bytes(w.batch, w.q_heads, w.kv_heads, w.head_dim, w.block_size,
                                           table.shape[1], args.chunk_tokens),
                      dtype=torch.uint8, device=dev)
     out2 = torch.empty_like(q)

@@ -72,10 +72,18 @@ GQA_B200_API int gqa_b200_abi_version(void);
 /* Text for a status code returned by any entry point (static storage). */
 GQA_B200_API const char* gqa_b200_strerror(int code);
 
+/* Base KV-chunk length (tokens) that chunk_tokens = 0 stands for.  Chosen from
+ * the static shape and the B200 SM count alone, never from context_lens: the
+ * largest of 1024 .. 64 that still cuts a full block table into several work
+ * items per resident CTA. */
+GQA_B200_API int gqa_b200_auto_chunk_tokens(int batch, int q_heads, int kv_heads, int block_size,
+                                            int max_pages);
+
 /* KV-chunk length, in tokens, that a sequence of `context_len` tokens is cut
- * into.  A function of the sequence's own length only (so a sequence is cut the
- * same way whichever batch or GPU it lands on).  chunk_tokens = 0 picks the
- * built-in base.  Long sequences use 2x and 4x the base. */
+ * into for a given base `chunk_tokens` (16 .. 65536).  A function of the
+ * sequence's own length only, so with one base a sequence is cut, and its
+ * partials merged, the same way whichever batch or GPU it lands on.  Sequences
+ * longer than 32x / 128x the base use 2x / 4x the base. */
 GQA_B200_API int gqa_b200_chunk_tokens(int context_len, int chunk_tokens);
 
 /* Upper bound on chunks per sequence for a table of max_pages*block_size tokens. */
@@ -85,8 +93,8 @@ GQA_B200_API int gqa_b200_max_chunks_per_seq(int max_pages, int block_size, int 
  * shape (worst case over context_lens).  The buffer must be 256-byte aligned.
  * Its contents need no initialisation and carry nothing between calls; two
  * calls that may overlap on the device need two workspaces. */
-GQA_B200_API size_t gqa_b200_workspace_bytes(int batch, int q_heads, int head_dim, int block_size,
-                                             int max_pages, int chunk_tokens);
+GQA_B200_API size_t gqa_b200_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim,
+                                             int block_size, int max_pages, int chunk_tokens);
 
 /* Paged single-token MHA/MQA/GQA decode.
  * Replaces gqa_decode_cuda (csrc/binding/torch_ops.cpp:5-11,

@@ -143,7 +143,7 @@ def test_out_and_workspace_arguments():
     args = _cuda(q, k, v, table, lens)
     want = _oracle(*args)
     out = torch.full_like(args[0], float("nan"))
-    need = attn.workspace_bytes(3, 8, 128, 16, table.shape[1], 64)
+    need = attn.workspace_bytes(3, 8, 2, 128, 16, table.shape[1], 64)
     ws = torch.empty(need, dtype=torch.uint8, device=DEV)
     res = attn.gqa_decode(*args, out=out, workspace=ws, chunk_tokens=64)
     assert res is out

@@ -43,10 +43,17 @@ def test_strerror_covers_every_status_code():
 def test_chunk_policy_depends_only_on_length():
     lib = _cabi.load()
     f = lib.gqa_b200_chunk_tokens
-    assert f(1, 0) == 512 and f(16384, 0) == 512 and f(16385, 0) == 1024
-    assert f(65536, 0) == 1024 and f(65537, 0) == 2048 and f(131072, 0) == 2048
+    assert f(1, 512) == 512 and f(16384, 512) == 512 and f(16385, 512) == 1024
+    assert f(65536, 512) == 1024 and f(65537, 512) == 2048 and f(131072, 512) == 2048
     assert f(100, 64) == 64 and f(64 * 32 + 1, 64) == 128
-    assert f(5, 8) < 0 and f(5, 1 << 20) < 0          # out-of-range base
+    assert f(5, 8) < 0 and f(5, 1 << 20) < 0 and f(5, 0) < 0      # out-of-range base
+    auto = lib.gqa_b200_auto_chunk_tokens
+    assert auto(64, 32, 8, 16, 254) == 1024         # big batch: long chunks
+    assert auto(128, 28, 4, 16, 128) == 512
+    assert auto(1, 32, 8, 16, 256) == 64            # one short sequence: cut finely
+    assert auto(1, 64, 8, 32, 4096) == 512
+    assert auto(4, 32, 8, 16, 32) == 64
+    assert auto(2, 7, 2, 16, 4) < 0                 # heads not divisible
 
 
 def test_max_chunks_bound_is_a_true_upper_bound():
@@ -65,10 +72,10 @@ def test_max_chunks_bound_is_a_true_upper_bound():
 
 
 def test_workspace_bytes_grows_with_shape_and_is_aligned():
-    a = attn.workspace_bytes(64, 32, 128, 16, 254)
-    b = attn.workspace_bytes(128, 32, 128, 16, 254)
+    a = attn.workspace_bytes(64, 32, 8, 128, 16, 254)
+    b = attn.workspace_bytes(128, 32, 8, 128, 16, 254)
     assert a % 256 == 0 and b > a > 0
-    assert attn.workspace_bytes(4, 8, 128, 16, 4, 16) > attn.workspace_bytes(4, 8, 128, 16, 4, 512)
+    assert attn.workspace_bytes(4, 8, 2, 128, 16, 4, 16) > attn.workspace_bytes(4, 8, 2, 128, 16, 4, 512)
 
 
 def test_compute_entry_points_reject_bad_arguments_without_a_gpu():
