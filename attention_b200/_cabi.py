@@ -21,6 +21,7 @@ SIGNATURES = {
                                                           c_size_t, _P]),
     "gqa_b200_decode_ex": (c_int, [_P] * 6 + [c_int] * 5 + [c_int64, c_int, c_int, c_float, _P,
                                                              c_size_t, _P, c_int, c_int, c_int, c_int]),
+    "gqa_b200_decode_static": (c_int, [_P] * 6 + [c_int] * 5 + [c_int64, c_int, c_int, c_float, _P]),
     "gqa_b200_decode_split": (c_int, [_P] * 6 + [c_int] * 5 + [c_int64, c_int, c_int, c_float,
                                                                 c_int, _P, _P]),
     "gqa_b200_kv_append": (c_int, [_P] * 6 + [c_int] * 4 + [c_int64, c_int, c_int, _P]),

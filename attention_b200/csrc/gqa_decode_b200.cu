@@ -411,6 +411,9 @@ const char* gqa_b200_strerror(int code) {
         case GQA_B200_ERR_KERNEL: return "the requested kernel cannot run these arguments";
         case GQA_B200_ERR_CHUNK: return "chunk_tokens must be 0 or in [16, 65536]";
         case GQA_B200_ERR_INT32_RANGE: return "tensor sizes exceed int32 CUDA launch limits";
+        case GQA_B200_ERR_STATIC_LIMIT:
+            return "shape needs more scratch than gqa_b200_decode_static's built-in "
+                   "GQA_B200_STATIC_SCRATCH_BYTES; use gqa_b200_decode with a caller workspace";
         default: break;
     }
     if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
@@ -508,6 +511,60 @@ int gqa_b200_decode(const void* q, const void* k_cache, const void* v_cache,
     return gqa_b200_decode_ex(q, k_cache, v_cache, block_table, context_lens, out, dtype, batch,
                               q_heads, kv_heads, head_dim, num_blocks, block_size, max_pages, scale,
                               workspace, workspace_bytes, stream, 0, GQA_B200_KERNEL_AUTO, 0, 0);
+}
+
+// ---------------------------------------------------------------------------
+// Decode without any caller- or library-side allocation.
+// ---------------------------------------------------------------------------
+// Scratch of gqa_b200_decode_static: one fixed array in the module image, so it
+// exists on every GPU that loads this library from load until process exit.
+constexpr size_t kStaticScratchBytes = (size_t)GQA_B200_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch per device.  In host code the array's name
+// is only a handle for the runtime, not a device pointer; the address each GPU
+// gave its copy is asked for once, with that GPU current.
+static void* g_static_scratch_ptr[kMaxDevices];
+static std::mutex g_static_scratch_mutex;
+
+static cudaError_t static_scratch_address(void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (!g_static_scratch_ptr[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess) return e;
+        if (!ptr) return cudaErrorInvalidSymbol;
+        g_static_scratch_ptr[dev] = ptr;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return cudaSuccess;
+}
+
+int gqa_b200_decode_static(const void* q, const void* k_cache, const void* v_cache,
+                           const int32_t* block_table, const int32_t* context_lens, void* out,
+                           int dtype, int batch, int q_heads, int kv_heads, int head_dim,
+                           int64_t num_blocks, int block_size, int max_pages, float scale,
+                           void* stream) {
+    int rc = check_common(q, k_cache, v_cache, block_table, context_lens, out, dtype, batch,
+                          q_heads, kv_heads, head_dim, num_blocks, block_size, max_pages, scale);
+    if (rc != GQA_B200_OK) return rc;
+    if (batch == 0) return GQA_B200_OK;
+    const size_t need = gqa_b200_workspace_bytes(batch, q_heads, kv_heads, head_dim, block_size,
+                                                 max_pages, 0);
+    if (need == 0 || need > kStaticScratchBytes) return GQA_B200_ERR_STATIC_LIMIT;
+    void* scratch = nullptr;
+    const cudaError_t e = static_scratch_address(&scratch);
+    if (e != cudaSuccess) return (int)e;
+    // Nothing in the scratch has to start at zero: the plan kernel rewrites the
+    // header (work counter included), the item list and the prefix array on every
+    // call, and partial slots are written before the merge kernel reads them.
+    return gqa_b200_decode_ex(q, k_cache, v_cache, block_table, context_lens, out, dtype, batch,
+                              q_heads, kv_heads, head_dim, num_blocks, block_size, max_pages, scale,
+                              scratch, kStaticScratchBytes, stream, 0, GQA_B200_KERNEL_AUTO, 0, 0);
 }
 
 int gqa_b200_decode_split(const void* q, const void* k_cache, const void* v_cache,

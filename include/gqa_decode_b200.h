@@ -56,6 +56,7 @@ extern "C" {
 #define GQA_B200_ERR_KERNEL (-11)     /* requested kernel cannot run these arguments */
 #define GQA_B200_ERR_CHUNK (-12)      /* chunk_tokens out of range              */
 #define GQA_B200_ERR_INT32_RANGE (-13)/* tensor sizes exceed int32 launch limits */
+#define GQA_B200_ERR_STATIC_LIMIT (-14) /* shape needs more than GQA_B200_STATIC_SCRATCH_BYTES */
 
 /* Workspace header: the first int32 words of the workspace, readable by the
  * host after a stream synchronise when debugging.
@@ -133,6 +134,43 @@ GQA_B200_API int gqa_b200_decode_ex(const void* q, const void* k_cache, const vo
                                     int max_pages, float scale, void* workspace,
                                     size_t workspace_bytes, void* stream, int chunk_tokens,
                                     int kernel, int max_ctas, int phases);
+
+/* Size of the scratch array built into the library for gqa_b200_decode_static. */
+#define GQA_B200_STATIC_SCRATCH_BYTES (8u << 20)
+
+/* gqa_b200_decode for callers that can hand over no scratch at all.  It has no
+ * counterpart in the reference library.
+ *
+ * Who needs it: a serving engine that has already given all free HBM to its KV
+ * page pool, where a later cudaMalloc can fail or fragment; a decode loop that
+ * must not stall, since cudaMalloc / cudaFree synchronise the whole device; a
+ * plug-in hosted by a runtime that owns device memory and forbids allocations
+ * behind its back.  Such a caller still passes its inputs and `out`; the chunk
+ * list and the split partials go to a fixed array of
+ * GQA_B200_STATIC_SCRATCH_BYTES (8 MiB) that is part of the library image, so
+ * every GPU that loads the library holds that much until the process exits.
+ *
+ * The call allocates and frees nothing (no cudaMalloc/cudaFree, no allocating
+ * library routine) and runs the same three kernels as gqa_b200_decode, so the
+ * result is identical.  Limits and rules:
+ *   - a shape whose gqa_b200_workspace_bytes(..., chunk_tokens = 0) exceeds
+ *     GQA_B200_STATIC_SCRATCH_BYTES is refused with GQA_B200_ERR_STATIC_LIMIT
+ *     and nothing is launched (for scale: batch 64, 32 query heads, head_dim
+ *     128, tables of 4096 tokens need about 4.3 MB);
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call
+ *     outside any stream capture;
+ *   - all calls on a device share the one array, which keeps whatever the last
+ *     call left in it.  Nothing in it has to be cleared by the caller (the plan
+ *     kernel rewrites the header, work counter included, every call), but two
+ *     calls that may run at the same time on the GPU -- different streams, or
+ *     different host threads -- race on it: serialise them, or give the
+ *     concurrent ones gqa_b200_decode with workspaces of their own. */
+GQA_B200_API int gqa_b200_decode_static(const void* q, const void* k_cache, const void* v_cache,
+                                        const int32_t* block_table, const int32_t* context_lens,
+                                        void* out, int dtype, int batch, int q_heads,
+                                        int kv_heads, int head_dim, int64_t num_blocks,
+                                        int block_size, int max_pages, float scale, void* stream);
 
 /* Decode with a caller-chosen number of KV partitions and the reference's
  * partial layout.  Replaces gqa_decode_split_cuda and

@@ -1,0 +1,94 @@
+"""gqa_b200_decode_static: the entry point for callers that cannot allocate.
+
+Some users of the C ABI have no scratch to give: all free HBM already belongs to
+their KV page pool, or they sit in a decode loop where cudaMalloc's device-wide
+synchronisation is not acceptable, or their host runtime owns device memory.
+For them the library carries an 8 MiB scratch array of its own.  This test calls
+that entry point directly through the C ABI, twice in a row on different inputs
+(the array is shared and keeps the previous call's contents), and checks each
+result against the ordinary entry point, which gets a workspace from the caller.
+It also checks that a shape too large for the built-in array is refused cleanly.
+
+The file name sorts last on purpose: with ``-x`` every other test has already
+run when this one does.  It does not depend on them and passes on its own.
+"""
+
+import pytest
+import torch
+
+from conftest import TOL
+
+from attention_b200 import _cabi, synth
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+STATIC_LIMIT = -14
+
+
+def _args(q, k, v, table, lens, out):
+    return (q.data_ptr(), k.data_ptr(), v.data_ptr(), table.data_ptr(), lens.data_ptr(),
+            out.data_ptr(), DTYPE_CODE[q.dtype], q.size(0), q.size(1), k.size(2), q.size(2),
+            k.size(0), k.size(1), table.size(1), 1.0 / q.size(2) ** 0.5)
+
+
+def _decode_with_caller_workspace(lib, q, k, v, table, lens):
+    out = torch.empty_like(q)
+    need = lib.gqa_b200_workspace_bytes(q.size(0), q.size(1), k.size(2), q.size(2), k.size(1),
+                                        table.size(1), 0)
+    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    rc = lib.gqa_b200_decode(*_args(q, k, v, table, lens, out), ws.data_ptr(), ws.numel(), stream)
+    assert rc == 0, _cabi.strerror(rc)
+    return out
+
+
+def _decode_static(lib, q, k, v, table, lens):
+    out = torch.full_like(q, float("nan"))
+    stream = torch.cuda.current_stream().cuda_stream
+    rc = lib.gqa_b200_decode_static(*_args(q, k, v, table, lens, out), stream)
+    return rc, out
+
+
+def test_static_scratch_entry_point_matches_the_ordinary_one_twice_in_a_row():
+    lib = _cabi.load()
+    cases = [
+        synth.scaled("c2_qwen3_8b_bf16", batch=6, len_lo=200, len_hi=3000),   # several chunks each
+        synth.scaled("c3_qwen25_7b_fp16", batch=9, len_lo=1, len_hi=700),     # different shape next
+        synth.scaled("c1_cpu_fp32", batch=3, len_lo=64, len_hi=400, fixed_pool_blocks=0),
+    ]
+    for i, w in enumerate(cases):
+        inputs = synth.make_workload(w, seed=100 + i, device=DEV, kv_on_device=True)
+        want = _decode_with_caller_workspace(lib, *inputs)
+        rc, got = _decode_static(lib, *inputs)
+        assert rc == 0, _cabi.strerror(rc)
+        torch.cuda.synchronize()
+        tol = TOL[w.dtype]
+        torch.testing.assert_close(got.float(), want.float(), atol=tol, rtol=tol)
+        # same inputs again straight away: stale scratch from the call before must not matter
+        rc, again = _decode_static(lib, *inputs)
+        assert rc == 0
+        torch.cuda.synchronize()
+        torch.testing.assert_close(again.float(), want.float(), atol=tol, rtol=tol)
+
+
+def test_static_scratch_entry_point_refuses_shapes_beyond_its_limit():
+    lib = _cabi.load()
+    w = synth.scaled("c2_qwen3_8b_bf16", batch=2, len_lo=20, len_hi=40)
+    q, k, v, table, lens = synth.make_workload(w, seed=1, device=DEV, kv_on_device=True)
+    # a wide table: the worst-case scratch for 2 x 4M-token tables is far beyond 8 MiB
+    wide = torch.full((2, 1 << 18), -1, dtype=torch.int32, device=DEV)
+    wide[:, : table.size(1)] = table
+    need = lib.gqa_b200_workspace_bytes(2, w.q_heads, w.kv_heads, w.head_dim, w.block_size,
+                                        wide.size(1), 0)
+    assert need > (8 << 20)
+    rc, out = _decode_static(lib, q, k, v, wide, lens)
+    assert rc == STATIC_LIMIT
+    assert "GQA_B200_STATIC_SCRATCH_BYTES" in _cabi.strerror(rc)
+    torch.cuda.synchronize()
+    assert torch.isnan(out.float()).all()          # nothing was launched
+    # the same sequences through a table of ordinary width are accepted
+    rc, out = _decode_static(lib, q, k, v, table, lens)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
