@@ -67,6 +67,7 @@ struct DecodeParams {
     float2* part_ml;        // [cap_chunks * q_heads] (max in log2 units, sum)
     float* part_acc;        // [cap_chunks * q_heads * head_dim]
     int cap_chunks;
+    int slots_per_seq;      // partial slot of (sequence b, chunk c) is b * slots_per_seq + c
     // reference-split mode
     float* ref_partials;    // [batch, q_heads, splits, head_dim + 2]
     int splits;
@@ -140,7 +141,7 @@ __device__ __forceinline__ WorkItem item_from_record(const DecodeParams& p, int 
     w.t1 = rec.w;
     if (p.mode == kModePlanned) {
         w.n_parts = (rec.y & kSingleFlag) ? 1 : 2;   // only "one" vs "several" matters here
-        w.part_slot = w.part;                         // chunk_off[b] + chunk index
+        w.part_slot = w.part;                         // b * slots_per_seq + chunk index
     } else {
         w.n_parts = p.splits;
         w.part_slot = 0;

@@ -66,6 +66,7 @@ WorkspaceLayout workspace_layout(int batch, int q_heads, int head_dim, int block
     const long long per_seq = max_chunks_for_capacity(cap_tokens, chunk_base);
     long long cap = per_seq * (batch > 0 ? batch : 0);
     if (cap > 0x3fffffffll) cap = 0x3fffffffll;   // bit 30 of a slot is the single-chunk flag
+                                                  // (decode_ex refuses shapes that hit this)
     w.cap_chunks = (int)cap;
     w.max_chunks_per_seq = (int)(per_seq > 0x7fffffffll ? 0x7fffffffll : per_seq);
     size_t at = 0;
@@ -466,6 +467,7 @@ int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
     if (batch == 0) return GQA_B200_OK;
 
     const WorkspaceLayout lay = workspace_layout(batch, q_heads, head_dim, block_size, max_pages, base);
+    if ((long long)lay.max_chunks_per_seq * batch > 0x3fffffffll) return GQA_B200_ERR_INT32_RANGE;
     if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < lay.total)
         return GQA_B200_ERR_WORKSPACE;
 
@@ -479,6 +481,7 @@ int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
     p.part_ml = reinterpret_cast<float2*>(ws + lay.part_ml);
     p.part_acc = reinterpret_cast<float*>(ws + lay.part_acc);
     p.cap_chunks = lay.cap_chunks;
+    p.slots_per_seq = lay.max_chunks_per_seq;
     p.mode = kModePlanned;
     p.splits = 1;
     p.chunk_base = base;

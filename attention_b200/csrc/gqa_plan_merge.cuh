@@ -34,8 +34,8 @@ __device__ __forceinline__ int plan_block_scan(int x, int* s_warp, int& total) {
 }
 
 // One CTA.  Reads context_lens and writes, without any host read of the lengths:
-//   chunk_off[b]  exclusive prefix of chunks per sequence (the partial slots of
-//                 sequence b are chunk_off[b] .. chunk_off[b+1]-1)
+//   chunk_off[b]  exclusive prefix of chunks per sequence (position of the
+//                 sequence's records in the item list)
 //   items[]       one record per chunk, in sequence order.  (Putting all short
 //                 last chunks at the end of the list was measured slower: equal
 //                 items make every CTA start and drain its copy pipeline at the
@@ -58,11 +58,12 @@ __global__ void __launch_bounds__(kPlanThreads) gqa_plan_kernel(const DecodePara
             p.chunk_off[b] = co;
             const int ct = chunk_tokens_for(len, p.chunk_base);
             const int flag = n == 1 ? kSingleFlag : 0;
-            for (int c = 0; c < n; ++c) {
+            const int slot0 = b * p.slots_per_seq;
+            for (int c = 0; c < n && c < p.slots_per_seq; ++c) {
                 const long long t0 = (long long)c * ct;
                 const int t1 = (int)(t0 + ct < len ? t0 + ct : len);
                 if (co + c < p.cap_chunks)
-                    p.items[co + c] = make_int4(b, (co + c) | flag, (int)t0, t1);
+                    p.items[co + c] = make_int4(b, (slot0 + c) | flag, (int)t0, t1);
             }
         }
         run_n += tot_n;
@@ -97,10 +98,9 @@ __global__ void __launch_bounds__(kMergeWarps * 32) gqa_merge_kernel(const Decod
     int n_parts;
     size_t first_slot = 0;
     if (p.mode == kModePlanned) {
-        const int c0 = p.chunk_off[b];
-        n_parts = p.chunk_off[b + 1] - c0;
-        if (c0 + n_parts > p.cap_chunks) n_parts = p.cap_chunks > c0 ? p.cap_chunks - c0 : 0;
-        first_slot = (size_t)c0;
+        n_parts = chunks_for(clamp_len(p, b), p.chunk_base);
+        if (n_parts > p.slots_per_seq) n_parts = p.slots_per_seq;
+        first_slot = (size_t)b * p.slots_per_seq;
         if (n_parts == 1) return;
     } else {
         n_parts = p.splits;
@@ -190,8 +190,11 @@ __global__ void __launch_bounds__(kMergeWarps * 32) gqa_merge_kernel(const Decod
 }
 
 // Planned-mode merge for short sequences (few chunks each): one WARP per
-// (sequence, query head), four pairs per CTA; lanes own float4 columns and the
-// chunk loop is unrolled so several partial rows are in flight.  head_dim % 4 == 0.
+// (sequence, query head), four pairs per CTA; lanes own float4 columns.  The
+// chunk count comes from the sequence's own length (one load), the partial
+// slots are at a fixed place per sequence, and four partial rows are fetched at
+// a time, so a sequence of up to four chunks costs two dependent memory round
+// trips.  Batches are folded with a running max.  head_dim % 4 == 0.
 template <typename T>
 __global__ void __launch_bounds__(kMergeWarps * 32) gqa_merge_warp_kernel(const DecodeParams p) {
     pdl_launch_dependents();
@@ -201,12 +204,12 @@ __global__ void __launch_bounds__(kMergeWarps * 32) gqa_merge_warp_kernel(const 
     if (pair >= (long long)p.batch * p.q_heads) return;
     const int b = (int)(pair / p.q_heads), hq = (int)(pair - (long long)b * p.q_heads);
     const int D = p.head_dim;
-    const int c0 = p.chunk_off[b];
-    int n = p.chunk_off[b + 1] - c0;
-    if (c0 + n > p.cap_chunks) n = p.cap_chunks > c0 ? p.cap_chunks - c0 : 0;
+    int n = chunks_for(clamp_len(p, b), p.chunk_base);
+    if (n > p.slots_per_seq) n = p.slots_per_seq;
     if (n == 1) return;
     T* out = reinterpret_cast<T*>(p.out) + ((size_t)b * p.q_heads + hq) * D;
     const int col0 = lane * 4, col1 = (32 + lane) * 4;
+    const bool use0 = col0 < D, use1 = col1 < D;
     auto store4 = [&](int col, float x0, float x1, float x2, float x3) {
         if (sizeof(T) == 4) {
             *reinterpret_cast<float4*>(out + col) = make_float4(x0, x1, x2, x3);
@@ -216,40 +219,48 @@ __global__ void __launch_bounds__(kMergeWarps * 32) gqa_merge_warp_kernel(const 
         }
     };
     if (n == 0) {
-        if (col0 < D) store4(col0, 0.f, 0.f, 0.f, 0.f);
-        if (col1 < D) store4(col1, 0.f, 0.f, 0.f, 0.f);
+        if (use0) store4(col0, 0.f, 0.f, 0.f, 0.f);
+        if (use1) store4(col1, 0.f, 0.f, 0.f, 0.f);
         return;
     }
-    const float2* ml = p.part_ml + (size_t)c0 * p.q_heads + hq;
-    const float* acc = p.part_acc + ((size_t)c0 * p.q_heads + hq) * D;
+    const size_t slot0 = (size_t)b * p.slots_per_seq;
+    const float2* ml = p.part_ml + slot0 * p.q_heads + hq;
+    const float* acc = p.part_acc + (slot0 * p.q_heads + hq) * D;
     const size_t ml_step = p.q_heads, acc_step = (size_t)p.q_heads * D;
-    float mx = -INFINITY;
-    for (int c = lane; c < n; c += 32) {
-        const float2 v = ml[c * ml_step];
-        if (v.y > 0.f) mx = fmaxf(mx, v.x);
-    }
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 a0 = zero4, a1 = zero4;
+    float mx = -INFINITY, sum = 0.f;
+    for (int c0 = 0; c0 < n; c0 += 4) {
+        float2 v[4];
+        float4 x0[4], x1[4];
 #pragma unroll
-    for (int d = 16; d >= 1; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
-    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
-    float sum = 0.f;
-#pragma unroll 4
-    for (int c = 0; c < n; ++c) {
-        const float2 v = ml[c * ml_step];
-        const float wgt = v.y > 0.f ? fast_exp2(v.x - mx) : 0.f;
-        sum += wgt * v.y;
-        const float* src = acc + c * acc_step;
-        if (col0 < D) {
-            const float4 x = *reinterpret_cast<const float4*>(src + col0);
-            a0.x += wgt * x.x; a0.y += wgt * x.y; a0.z += wgt * x.z; a0.w += wgt * x.w;
+        for (int j = 0; j < 4; ++j) {
+            const bool live = c0 + j < n;
+            v[j] = live ? ml[(c0 + j) * ml_step] : make_float2(-INFINITY, 0.f);
+            const float* src = acc + (c0 + j) * acc_step;
+            x0[j] = live && use0 ? *reinterpret_cast<const float4*>(src + col0) : zero4;
+            x1[j] = live && use1 ? *reinterpret_cast<const float4*>(src + col1) : zero4;
         }
-        if (col1 < D) {
-            const float4 x = *reinterpret_cast<const float4*>(src + col1);
-            a1.x += wgt * x.x; a1.y += wgt * x.y; a1.z += wgt * x.z; a1.w += wgt * x.w;
+        float bm = mx;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (v[j].y > 0.f) bm = fmaxf(bm, v[j].x);
+        const float r = sum > 0.f ? fast_exp2(mx - bm) : 0.f;
+        sum *= r;
+        a0.x *= r; a0.y *= r; a0.z *= r; a0.w *= r;
+        a1.x *= r; a1.y *= r; a1.z *= r; a1.w *= r;
+        mx = bm;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float wgt = v[j].y > 0.f ? fast_exp2(v[j].x - mx) : 0.f;
+            sum += wgt * v[j].y;
+            a0.x += wgt * x0[j].x; a0.y += wgt * x0[j].y; a0.z += wgt * x0[j].z; a0.w += wgt * x0[j].w;
+            a1.x += wgt * x1[j].x; a1.y += wgt * x1[j].y; a1.z += wgt * x1[j].z; a1.w += wgt * x1[j].w;
         }
     }
     const float inv = sum > 0.f ? 1.f / sum : 0.f;
-    if (col0 < D) store4(col0, a0.x * inv, a0.y * inv, a0.z * inv, a0.w * inv);
-    if (col1 < D) store4(col1, a1.x * inv, a1.y * inv, a1.z * inv, a1.w * inv);
+    if (use0) store4(col0, a0.x * inv, a0.y * inv, a0.z * inv, a0.w * inv);
+    if (use1) store4(col1, a1.x * inv, a1.y * inv, a1.z * inv, a1.w * inv);
 }
 
 }  // namespace gqa_b200
