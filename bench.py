@@ -39,7 +39,7 @@ DTYPE_NAME = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"
 
 # DRAM bytes (read + write) per decode-kernel launch from the ncu capture summarised
 # under profiles/, as a ratio to the algorithmic bytes of the captured case.
-NCU_TRAFFIC_RATIO = {}
+NCU_TRAFFIC_RATIO = {"c2_qwen3_8b_bf16": 1.010}
 
 
 def parse_args():
