@@ -253,12 +253,12 @@ cudaError_t launch_persistent(KernelT kernel, const DecodeParams& p, int threads
     return launch_kernel(kernel, dim3((unsigned)grid), threads, smem, stream, p);
 }
 
-template <typename T, int D, int TILE_N, int NSTAGES, int MIN_CTAS, int NWARPS = 4>
+template <typename T, int D, int TILE_N, int NSTAGES, int MIN_CTAS, int NWARPS = 4, int CP_MODE = 3>
 cudaError_t launch_mma(const DecodeParams& p, int max_ctas, long long item_bound,
                        cudaStream_t stream) {
     using G = MmaGeom<D, TILE_N, NSTAGES, NWARPS>;
     const size_t smem = G::kFixedBytes + (size_t)p.table_smem_entries * sizeof(int);
-    return launch_persistent(gqa_decode_mma_kernel<T, D, TILE_N, NSTAGES, NWARPS, MIN_CTAS>, p,
+    return launch_persistent(gqa_decode_mma_kernel<T, D, TILE_N, NSTAGES, NWARPS, MIN_CTAS, CP_MODE>, p,
                              NWARPS * 32, smem, max_ctas, item_bound, stream);
 }
 
@@ -276,6 +276,8 @@ cudaError_t launch_mma_for_dim(const DecodeParams& p, int max_ctas, long long it
                 case 4: return launch_mma<T, 128, 16, 4, 1, 6>(p, max_ctas, item_bound, stream);
                 case 5: return launch_mma<T, 128, 16, 2, 2>(p, max_ctas, item_bound, stream);
                 case 6: return launch_mma<T, 128, 32, 3, 1>(p, max_ctas, item_bound, stream);
+                case 10: return launch_mma<T, 128, 16, 3, 2, 4, 0>(p, max_ctas, item_bound, stream);
+                case 14: return launch_mma<T, 128, 16, 3, 2, 4, 4>(p, max_ctas, item_bound, stream);
                 default: break;
             }
 #endif

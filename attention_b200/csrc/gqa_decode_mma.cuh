@@ -53,10 +53,36 @@ template <> struct MmaOps<__nv_bfloat16> {
     }
 };
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src),
-                 "r"(src_bytes)
-                 : "memory");
+// 16-byte asynchronous global->shared copy that bypasses L1; bytes beyond
+// src_bytes are zero-filled.  CP_MODE selects an L2 hint: 0 none, 1 prefetch the
+// 128-byte line, 2 prefetch 256 bytes, 3 = 2 plus an evict-first policy, 4 =
+// evict-first only.  K/V rows are read exactly once per call, so keeping them
+// out of L2's retained set leaves it to the partials, tables and queries
+// (measured: 2-4 % faster calls than no hint; the prefetch sizes alone: no change).
+template <int CP_MODE>
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes,
+                                           uint64_t policy) {
+    if (CP_MODE == 1) {
+        asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;\n" ::"r"(dst),
+                     "l"(src), "r"(src_bytes) : "memory");
+    } else if (CP_MODE == 2) {
+        asm volatile("cp.async.cg.shared.global.L2::256B [%0], [%1], 16, %2;\n" ::"r"(dst),
+                     "l"(src), "r"(src_bytes) : "memory");
+    } else if (CP_MODE == 3) {
+        asm volatile("cp.async.cg.shared.global.L2::cache_hint.L2::256B [%0], [%1], 16, %2, %3;\n"
+                     ::"r"(dst), "l"(src), "r"(src_bytes), "l"(policy) : "memory");
+    } else if (CP_MODE == 4) {
+        asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;\n"
+                     ::"r"(dst), "l"(src), "r"(src_bytes), "l"(policy) : "memory");
+    } else {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src),
+                     "r"(src_bytes) : "memory");
+    }
+}
+__device__ __forceinline__ uint64_t evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
 }
 __device__ __forceinline__ void cp_async_commit() {
     asm volatile("cp.async.commit_group;\n" ::: "memory");
@@ -102,7 +128,7 @@ template <int D, int TILE_N, int NSTAGES, int NWARPS> struct MmaGeom {
 // the normalised result is unchanged.
 constexpr float kRescaleSlack = 8.f;
 
-template <typename T, int D, int TILE_N, int NSTAGES, int NWARPS, int MIN_CTAS>
+template <typename T, int D, int TILE_N, int NSTAGES, int NWARPS, int MIN_CTAS, int CP_MODE = 3>
 __global__ void __launch_bounds__(NWARPS * 32, MIN_CTAS)
 gqa_decode_mma_kernel(const DecodeParams p) {
     using G = MmaGeom<D, TILE_N, NSTAGES, NWARPS>;
@@ -137,6 +163,7 @@ gqa_decode_mma_kernel(const DecodeParams p) {
     const char* vc = reinterpret_cast<const char*>(p.v);
     const T* qp = reinterpret_cast<const T*>(p.q);
     const long long row_bytes_all = (long long)p.kv_heads * ROWB;   // one token, all kv heads
+    const uint64_t policy = CP_MODE >= 3 ? evict_first_policy() : 0;
     pdl_launch_dependents();
     pdl_wait();   // the plan kernel wrote hdr / items
     const int n_items = total_items(p);
@@ -239,8 +266,8 @@ gqa_decode_mma_kernel(const DecodeParams p) {
                                 for (int it = 0; it < SUB_ITERS; ++it) {
                                     const int row = sub * 16 + it * ROWS_PER_IT + ld_row;
                                     const uint32_t dst = row * ROWB + ((ld_cc ^ (row & 7)) << 4);
-                                    cp_async16(sk + dst, ks, 16);
-                                    cp_async16(sv + dst, vs, 16);
+                                    cp_async16<CP_MODE>(sk + dst, ks, 16, policy);
+                                    cp_async16<CP_MODE>(sv + dst, vs, 16, policy);
                                     ks += ROWS_PER_IT * row_bytes_all;
                                     vs += ROWS_PER_IT * row_bytes_all;
                                 }
@@ -260,8 +287,8 @@ gqa_decode_mma_kernel(const DecodeParams p) {
                                           (long long)w.kvh * ROWB + ld_cc * 16;
                                 }
                                 const uint32_t dst = row * ROWB + ((ld_cc ^ (row & 7)) << 4);
-                                cp_async16(sk + dst, kc + off, valid ? 16 : 0);
-                                cp_async16(sv + dst, vc + off, valid ? 16 : 0);
+                                cp_async16<CP_MODE>(sk + dst, kc + off, valid ? 16 : 0, policy);
+                                cp_async16<CP_MODE>(sv + dst, vc + off, valid ? 16 : 0, policy);
                             }
                         }
                     }
