@@ -87,13 +87,71 @@ def _raise_status(rc: int, what: str) -> None:
         raise RuntimeError(f"{what} failed: {_cabi.strerror(rc)} (status {rc})")
 
 
+try:   # raw handle of the current stream without building a Stream object (a few us less)
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+except AttributeError:   # pragma: no cover - older/newer torch without the private hook
+    _raw_stream = None
+
+
 def _stream_handle(device: torch.device) -> int:
+    if _raw_stream is not None:
+        return int(_raw_stream(device.index))
     return int(torch.cuda.current_stream(device).cuda_stream)
 
 
+class _on_device:
+    """``with _on_device(dev):`` makes ``dev`` current only if it is not already."""
+
+    __slots__ = ("_ctx",)
+
+    def __init__(self, device: torch.device):
+        self._ctx = None if torch.cuda.current_device() == device.index else torch.cuda.device(device)
+
+    def __enter__(self):
+        if self._ctx is not None:
+            self._ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self._ctx is not None:
+            self._ctx.__exit__(*exc)
+
+
+def _decode_inputs_ok(q, k_cache, v_cache, block_table, context_lens, scale) -> bool:
+    """One boolean for "every check of _validate_decode passes" (the common case); on False
+    the caller runs _validate_decode, which raises the specific message."""
+    try:
+        dt = q.dtype
+        dev = q.device
+        return (q.is_cuda and k_cache.is_cuda and v_cache.is_cuda and block_table.is_cuda
+                and context_lens.is_cuda
+                and q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
+                and block_table.is_contiguous() and context_lens.is_contiguous()
+                and q.dim() == 3 and k_cache.dim() == 4 and v_cache.shape == k_cache.shape
+                and block_table.dim() == 2 and context_lens.dim() == 1
+                and k_cache.device == dev and v_cache.device == dev
+                and block_table.device == dev and context_lens.device == dev
+                and k_cache.dtype == dt and v_cache.dtype == dt and dt in _DTYPE_CODE
+                and block_table.dtype == torch.int32 and context_lens.dtype == torch.int32
+                and q.size(0) == block_table.size(0) == context_lens.size(0)
+                and q.size(2) == k_cache.size(3) and q.size(1) > 0 and k_cache.size(2) > 0
+                and q.size(1) % k_cache.size(2) == 0 and 0 < q.size(2) <= 256
+                and k_cache.size(0) > 0 and k_cache.size(1) > 0 and block_table.size(1) > 0
+                and 0.0 < scale < math.inf
+                and max(q.size(0), q.size(1), k_cache.size(0), k_cache.size(1),
+                        block_table.size(1)) <= 2**31 - 1)
+    except (AttributeError, TypeError):
+        return False
+
+
+_ws_need: dict[tuple, int] = {}
+
+
 def _workspace_for(lib, q, kv_heads, block_size, max_pages, chunk_tokens, stream):
-    need = int(lib.gqa_b200_workspace_bytes(q.size(0), q.size(1), kv_heads, q.size(2), block_size,
-                                            max_pages, chunk_tokens))
+    shape_key = (q.size(0), q.size(1), kv_heads, q.size(2), block_size, max_pages, chunk_tokens)
+    need = _ws_need.get(shape_key)
+    if need is None:
+        need = int(lib.gqa_b200_workspace_bytes(*shape_key))
+        _ws_need[shape_key] = need
     key = (q.device.index, stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < need:
@@ -127,7 +185,9 @@ def gqa_decode(q, k_cache, v_cache, block_table, context_lens, *, scale=None, ou
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     scale = float(scale)
-    _validate_decode(q, k_cache, v_cache, block_table, context_lens, scale)
+    if not _decode_inputs_ok(q, k_cache, v_cache, block_table, context_lens, scale):
+        _validate_decode(q, k_cache, v_cache, block_table, context_lens, scale)
+        raise RuntimeError("invalid gqa_decode arguments")   # not reached: the line above raises
     if kernel not in _KERNEL_CODE:
         raise ValueError("kernel must be auto, simt or mma")
     if out is None:
@@ -138,7 +198,7 @@ def gqa_decode(q, k_cache, v_cache, block_table, context_lens, *, scale=None, ou
                "out must match q")
     if q.size(0) == 0:
         return out
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         stream = _stream_handle(q.device)
         if workspace is None:
             workspace, need = _workspace_for(lib, q, k_cache.size(2), k_cache.size(1),
@@ -187,7 +247,7 @@ def gqa_decode_split(q, k_cache, v_cache, block_table, context_lens, *, splits=4
     out = torch.empty_like(q)
     if q.size(0) == 0:
         return out
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         rc = lib.gqa_b200_decode_split(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
             context_lens.data_ptr(), out.data_ptr(), _DTYPE_CODE[q.dtype], q.size(0), q.size(1),
@@ -232,7 +292,7 @@ def kv_append(key, value, k_cache, v_cache, block_table, positions):
     _check(key.dtype in _DTYPE_CODE, "unsupported dtype")
     if key.size(0) == 0:
         return
-    with torch.cuda.device(key.device):
+    with _on_device(key.device):
         rc = lib.gqa_b200_kv_append(
             key.data_ptr(), value.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
             block_table.data_ptr(), positions.data_ptr(), _DTYPE_CODE[key.dtype], key.size(0),

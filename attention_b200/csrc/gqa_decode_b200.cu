@@ -81,10 +81,10 @@ WorkspaceLayout workspace_layout(int batch, int q_heads, int head_dim, int block
 
 // chunk_tokens == 0: pick the base chunk length from the static shape alone (no
 // read of context_lens): the largest of 1024 .. 64 that still cuts a full table
-// into at least kItemsPerSlot items per resident CTA, so small batches are split
-// finely enough to fill the GPU and large ones pay little per-item overhead.
+// into about one work item per resident CTA.  Large batches get long chunks
+// (little per-item overhead, few partials); small ones are cut finely enough to
+// occupy every SM in a single wave, which is what bounds their latency.
 constexpr int kAssumedCtaSlots = 2 * 148;   // B200: 148 SMs x 2 resident decode CTAs
-constexpr int kItemsPerSlot = 4;
 
 int auto_chunk_base(int batch, int q_heads, int kv_heads, int block_size, int max_pages) {
     const long long cap_tokens = (long long)max_pages * block_size;
@@ -92,7 +92,7 @@ int auto_chunk_base(int batch, int q_heads, int kv_heads, int block_size, int ma
     const long long per_chunk = (long long)batch * kv_heads * ((group + 15) / 16);
     for (int base = 1024; base > 64; base >>= 1) {
         const long long chunks = (cap_tokens + base - 1) / base;
-        if (per_chunk * chunks >= (long long)kItemsPerSlot * kAssumedCtaSlots) return base;
+        if (4 * per_chunk * chunks >= 3ll * kAssumedCtaSlots) return base;
     }
     return 64;
 }

@@ -272,6 +272,21 @@ gqa_decode_mma_kernel(const DecodeParams p) {
                                     vs += ROWS_PER_IT * row_bytes_all;
                                 }
                             }
+                        } else if (p.bs_shift >= 0 && tile_t0 + TILE_N <= s1) {
+                            // whole tile valid, power-of-two pages of any size (or an
+                            // unaligned start): one table lookup per row, no predicates
+#pragma unroll 2
+                            for (int it = 0; it < LD_ITERS; ++it) {
+                                const int row = it * ROWS_PER_IT + ld_row;
+                                const int t = tile_t0 + row;
+                                const long long phys = s_table[(t >> p.bs_shift) - first_page];
+                                const int slot = t & (p.block_size - 1);
+                                const long long off = (phys * p.block_size + slot) * row_bytes_all +
+                                                      (long long)w.kvh * ROWB + ld_cc * 16;
+                                const uint32_t dst = row * ROWB + ((ld_cc ^ (row & 7)) << 4);
+                                cp_async16<CP_MODE>(sk + dst, kc + off, 16, policy);
+                                cp_async16<CP_MODE>(sv + dst, vc + off, 16, policy);
+                            }
                         } else {
 #pragma unroll 1
                             for (int it = 0; it < LD_ITERS; ++it) {

@@ -75,8 +75,8 @@ GQA_B200_API const char* gqa_b200_strerror(int code);
 
 /* Base KV-chunk length (tokens) that chunk_tokens = 0 stands for.  Chosen from
  * the static shape and the B200 SM count alone, never from context_lens: the
- * largest of 1024 .. 64 that still cuts a full block table into several work
- * items per resident CTA. */
+ * largest of 1024 .. 64 that still cuts a full block table into about one work
+ * item per resident CTA. */
 GQA_B200_API int gqa_b200_auto_chunk_tokens(int batch, int q_heads, int kv_heads, int block_size,
                                             int max_pages);
 

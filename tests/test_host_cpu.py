@@ -49,10 +49,11 @@ def test_chunk_policy_depends_only_on_length():
     assert f(5, 8) < 0 and f(5, 1 << 20) < 0 and f(5, 0) < 0      # out-of-range base
     auto = lib.gqa_b200_auto_chunk_tokens
     assert auto(64, 32, 8, 16, 254) == 1024         # big batch: long chunks
-    assert auto(128, 28, 4, 16, 128) == 512
-    assert auto(1, 32, 8, 16, 256) == 64            # one short sequence: cut finely
-    assert auto(1, 64, 8, 32, 4096) == 512
-    assert auto(4, 32, 8, 16, 32) == 64
+    assert auto(128, 28, 4, 16, 128) == 1024
+    assert auto(1, 32, 8, 16, 512) == 256           # one 8k sequence: one wave of 256 items
+    assert auto(8, 32, 8, 16, 32) == 128
+    assert auto(1, 32, 8, 16, 16) == 64             # one short sequence: cut as finely as allowed
+    assert auto(1, 64, 8, 32, 4096) == 1024
     assert auto(2, 7, 2, 16, 4) < 0                 # heads not divisible
 
 
