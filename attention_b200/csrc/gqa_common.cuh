@@ -17,6 +17,8 @@ constexpr int kHdrWords = 64;           // int32 words reserved at the head of t
 constexpr int kHdrCounter = 0;
 constexpr int kHdrTotalChunks = 1;
 constexpr int kHdrStatus = 2;
+constexpr int kHdrChunkBase = 3;
+constexpr int kNumAutoBases = 5;        // adaptive base candidates: 1024 >> i, i = 0..4
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -67,7 +69,7 @@ struct DecodeParams {
     float2* part_ml;        // [cap_chunks * q_heads] (max in log2 units, sum)
     float* part_acc;        // [cap_chunks * q_heads * head_dim]
     int cap_chunks;
-    int slots_per_seq;      // partial slot of (sequence b, chunk c) is b * slots_per_seq + c
+    int item_target;        // adaptive base: smallest chunk total that fills the resident CTAs
     // reference-split mode
     float* ref_partials;    // [batch, q_heads, splits, head_dim + 2]
     int splits;
@@ -79,7 +81,7 @@ struct DecodeParams {
     int block_size, bs_shift, max_pages;
     long long num_blocks;
     int cap_tokens;         // min(max_pages * block_size, INT_MAX)
-    int chunk_base;
+    int chunk_base;         // base chunk length; 0 = the plan kernel picks it from the lengths
     int seg_tokens;         // tokens whose page ids are staged in shared memory at once
     int table_smem_entries; // seg_tokens / block_size + 2
     float scale_log2;       // scale * log2(e)
@@ -141,7 +143,7 @@ __device__ __forceinline__ WorkItem item_from_record(const DecodeParams& p, int 
     w.t1 = rec.w;
     if (p.mode == kModePlanned) {
         w.n_parts = (rec.y & kSingleFlag) ? 1 : 2;   // only "one" vs "several" matters here
-        w.part_slot = w.part;                         // b * slots_per_seq + chunk index
+        w.part_slot = w.part;                         // chunk_off[b] + chunk index
     } else {
         w.n_parts = p.splits;
         w.part_slot = 0;

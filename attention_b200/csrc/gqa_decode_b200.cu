@@ -21,7 +21,7 @@ namespace {
 
 constexpr int kTableEntriesBudget = 2048;   // page ids staged in shared memory per segment
 constexpr int kMaxDevices = 64;
-constexpr int kWarpMergeMaxChunks = 16;     // longer sequences use the CTA-per-head merge
+constexpr int kWarpMergeMinPairs = 1024;    // fewer (sequence, head) pairs: CTA-per-pair merge
 
 struct DeviceInfo {
     int sm_count = 0;
@@ -56,19 +56,41 @@ inline int elem_size(int dtype) { return dtype == GQA_B200_F32 ? 4 : 2; }
 struct WorkspaceLayout {
     size_t hdr, chunk_off, items, part_ml, part_acc, total;
     int cap_chunks;
-    int max_chunks_per_seq;
 };
 
-WorkspaceLayout workspace_layout(int batch, int q_heads, int head_dim, int block_size,
-                                 int max_pages, int chunk_base) {
+constexpr int kAssumedCtaSlots = 2 * 148;   // B200: 148 SMs x 2 resident decode CTAs
+
+// Chunk total at which the work items (chunks x kv heads x head groups) number about
+// three quarters of the resident decode CTAs: enough to occupy every SM in one wave.
+int item_target_chunks(int q_heads, int kv_heads) {
+    const int group = q_heads / kv_heads;
+    const long long per_chunk = (long long)kv_heads * ((group + 15) / 16);
+    const long long t = (3ll * kAssumedCtaSlots + 4 * per_chunk - 1) / (4 * per_chunk);
+    return (int)(t < 1 ? 1 : t);
+}
+
+// chunk_base == 0 (the plan kernel picks the base from the actual lengths): the chunk
+// total is at most that of base 1024 when 1024 is picked, and below twice the item
+// target otherwise (halving the base at most doubles a sequence's chunk count, and a
+// smaller base is only taken while the next larger one stays below the target).
+WorkspaceLayout workspace_layout(int batch, int q_heads, int kv_heads, int head_dim,
+                                 int block_size, int max_pages, int chunk_base) {
     WorkspaceLayout w{};
     const long long cap_tokens = (long long)max_pages * block_size;
-    const long long per_seq = max_chunks_for_capacity(cap_tokens, chunk_base);
-    long long cap = per_seq * (batch > 0 ? batch : 0);
+    const long long nb = batch > 0 ? batch : 0;
+    long long cap;
+    if (chunk_base == 0) {
+        cap = nb * max_chunks_for_capacity(cap_tokens, 1024);
+        const long long dyn = 2ll * item_target_chunks(q_heads, kv_heads) + nb;
+        const long long finest = nb * max_chunks_for_capacity(cap_tokens, 1024 >> (kNumAutoBases - 1));
+        const long long other = dyn < finest ? dyn : finest;
+        if (other > cap) cap = other;
+    } else {
+        cap = nb * max_chunks_for_capacity(cap_tokens, chunk_base);
+    }
     if (cap > 0x3fffffffll) cap = 0x3fffffffll;   // bit 30 of a slot is the single-chunk flag
                                                   // (decode_ex refuses shapes that hit this)
     w.cap_chunks = (int)cap;
-    w.max_chunks_per_seq = (int)(per_seq > 0x7fffffffll ? 0x7fffffffll : per_seq);
     size_t at = 0;
     w.hdr = at;        at = align_up(at + kHdrWords * sizeof(int32_t), 256);
     w.chunk_off = at;  at = align_up(at + ((size_t)batch + 1) * sizeof(int32_t), 256);
@@ -79,27 +101,22 @@ WorkspaceLayout workspace_layout(int batch, int q_heads, int head_dim, int block
     return w;
 }
 
-// chunk_tokens == 0: pick the base chunk length from the static shape alone (no
-// read of context_lens): the largest of 1024 .. 64 that still cuts a full table
-// into about one work item per resident CTA.  Large batches get long chunks
-// (little per-item overhead, few partials); small ones are cut finely enough to
-// occupy every SM in a single wave, which is what bounds their latency.
-constexpr int kAssumedCtaSlots = 2 * 148;   // B200: 148 SMs x 2 resident decode CTAs
-
+// What the plan kernel would pick if every sequence filled its table: a host-side
+// preview of the adaptive rule (the device applies it to the real lengths).
 int auto_chunk_base(int batch, int q_heads, int kv_heads, int block_size, int max_pages) {
     const long long cap_tokens = (long long)max_pages * block_size;
-    const int group = q_heads / kv_heads;
-    const long long per_chunk = (long long)batch * kv_heads * ((group + 15) / 16);
-    for (int base = 1024; base > 64; base >>= 1) {
-        const long long chunks = (cap_tokens + base - 1) / base;
-        if (4 * per_chunk * chunks >= 3ll * kAssumedCtaSlots) return base;
+    const int target = item_target_chunks(q_heads, kv_heads);
+    for (int i = 0; i < kNumAutoBases; ++i) {
+        const int base = 1024 >> i;
+        const int len = cap_tokens > 0x7fffffffll ? 0x7fffffff : (int)cap_tokens;
+        if ((long long)batch * chunks_for(len, base) >= target) return base;
     }
-    return 64;
+    return 1024 >> (kNumAutoBases - 1);
 }
 
-int resolve_chunk_base(int chunk_tokens, int batch, int q_heads, int kv_heads, int block_size,
-                       int max_pages) {
-    if (chunk_tokens == 0) return auto_chunk_base(batch, q_heads, kv_heads, block_size, max_pages);
+// 0 stays 0 (= adaptive, decided on the device); anything else must be in range.
+int resolve_chunk_base(int chunk_tokens) {
+    if (chunk_tokens == 0) return 0;
     if (chunk_tokens < kMinChunkTokens || chunk_tokens > kMaxChunkTokens) return -1;
     return chunk_tokens;
 }
@@ -367,10 +384,13 @@ cudaError_t launch_decode(DecodeParams& p, int dtype, bool use_mma, int max_ctas
     }
 }
 
+// Planned mode with head_dim % 4 == 0: one warp per (sequence, head) when there are
+// enough pairs to fill the GPU that way, else one CTA per pair (its four warps share a
+// long sequence's partials).
 template <typename T>
-cudaError_t launch_merge_t(const DecodeParams& p, int max_chunks_per_seq, cudaStream_t stream) {
+cudaError_t launch_merge_t(const DecodeParams& p, cudaStream_t stream) {
     const bool vec4 = p.mode == kModePlanned && p.head_dim % 4 == 0;
-    if (vec4 && max_chunks_per_seq <= kWarpMergeMaxChunks) {
+    if (vec4 && (long long)p.batch * p.q_heads >= kWarpMergeMinPairs) {
         const long long pairs = (long long)p.batch * p.q_heads;
         const unsigned grid = (unsigned)((pairs + kMergeWarps - 1) / kMergeWarps);
         return launch_kernel(gqa_merge_warp_kernel<T>, dim3(grid), kMergeWarps * 32, 0, stream, p);
@@ -380,12 +400,11 @@ cudaError_t launch_merge_t(const DecodeParams& p, int max_chunks_per_seq, cudaSt
     return launch_kernel(gqa_merge_kernel<T, false>, grid, kMergeWarps * 32, 0, stream, p);
 }
 
-cudaError_t launch_merge(const DecodeParams& p, int dtype, int max_chunks_per_seq,
-                         cudaStream_t stream) {
+cudaError_t launch_merge(const DecodeParams& p, int dtype, cudaStream_t stream) {
     switch (dtype) {
-        case GQA_B200_F32:  return launch_merge_t<float>(p, max_chunks_per_seq, stream);
-        case GQA_B200_F16:  return launch_merge_t<__half>(p, max_chunks_per_seq, stream);
-        default:            return launch_merge_t<__nv_bfloat16>(p, max_chunks_per_seq, stream);
+        case GQA_B200_F32:  return launch_merge_t<float>(p, stream);
+        case GQA_B200_F16:  return launch_merge_t<__half>(p, stream);
+        default:            return launch_merge_t<__nv_bfloat16>(p, stream);
     }
 }
 
@@ -447,9 +466,9 @@ size_t gqa_b200_workspace_bytes(int batch, int q_heads, int kv_heads, int head_d
     if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads || head_dim <= 0 ||
         block_size <= 0 || max_pages <= 0)
         return 0;
-    const int base = resolve_chunk_base(chunk_tokens, batch, q_heads, kv_heads, block_size, max_pages);
+    const int base = resolve_chunk_base(chunk_tokens);
     if (base < 0) return 0;
-    return workspace_layout(batch, q_heads, head_dim, block_size, max_pages, base).total;
+    return workspace_layout(batch, q_heads, kv_heads, head_dim, block_size, max_pages, base).total;
 }
 
 int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
@@ -461,15 +480,16 @@ int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
     int rc = check_common(q, k_cache, v_cache, block_table, context_lens, out, dtype, batch,
                           q_heads, kv_heads, head_dim, num_blocks, block_size, max_pages, scale);
     if (rc != GQA_B200_OK) return rc;
-    const int base = resolve_chunk_base(chunk_tokens, batch, q_heads, kv_heads, block_size, max_pages);
+    const int base = resolve_chunk_base(chunk_tokens);
     if (base < 0) return GQA_B200_ERR_CHUNK;
     if (kernel != GQA_B200_KERNEL_AUTO && kernel != GQA_B200_KERNEL_SIMT &&
         kernel != GQA_B200_KERNEL_MMA)
         return GQA_B200_ERR_KERNEL;
     if (batch == 0) return GQA_B200_OK;
 
-    const WorkspaceLayout lay = workspace_layout(batch, q_heads, head_dim, block_size, max_pages, base);
-    if ((long long)lay.max_chunks_per_seq * batch > 0x3fffffffll) return GQA_B200_ERR_INT32_RANGE;
+    const WorkspaceLayout lay =
+        workspace_layout(batch, q_heads, kv_heads, head_dim, block_size, max_pages, base);
+    if (lay.cap_chunks >= 0x3fffffff) return GQA_B200_ERR_INT32_RANGE;
     if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < lay.total)
         return GQA_B200_ERR_WORKSPACE;
 
@@ -483,11 +503,11 @@ int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
     p.part_ml = reinterpret_cast<float2*>(ws + lay.part_ml);
     p.part_acc = reinterpret_cast<float*>(ws + lay.part_acc);
     p.cap_chunks = lay.cap_chunks;
-    p.slots_per_seq = lay.max_chunks_per_seq;
+    p.item_target = item_target_chunks(q_heads, kv_heads);
     p.mode = kModePlanned;
     p.splits = 1;
     p.chunk_base = base;
-    set_segment(p, 4ll * base);
+    set_segment(p, 4ll * (base ? base : 1024));
 
     bool use_mma = mma_eligible(p, dtype);
     if (kernel == GQA_B200_KERNEL_MMA && !use_mma) return GQA_B200_ERR_KERNEL;
@@ -504,7 +524,7 @@ int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
         e = launch_decode(p, dtype, use_mma, max_ctas, s);
         if (e != cudaSuccess) return (int)e;
     }
-    if (phases & GQA_B200_PHASE_MERGE) e = launch_merge(p, dtype, lay.max_chunks_per_seq, s);
+    if (phases & GQA_B200_PHASE_MERGE) e = launch_merge(p, dtype, s);
     return (int)e;
 }
 
@@ -598,7 +618,7 @@ int gqa_b200_decode_split(const void* q, const void* k_cache, const void* v_cach
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e = launch_decode(p, dtype, use_mma, 0, s);
     if (e != cudaSuccess) return (int)e;
-    if (splits > 1) e = launch_merge(p, dtype, splits, s);
+    if (splits > 1) e = launch_merge(p, dtype, s);
     return (int)e;
 }
 

@@ -34,36 +34,74 @@ __device__ __forceinline__ int plan_block_scan(int x, int* s_warp, int& total) {
 }
 
 // One CTA.  Reads context_lens and writes, without any host read of the lengths:
-//   chunk_off[b]  exclusive prefix of chunks per sequence (position of the
-//                 sequence's records in the item list)
+//   the base chunk length, when the caller left it open (chunk_base == 0): the
+//                 largest of 1024, 512, ... 64 for which the batch's ACTUAL
+//                 lengths give at least item_target chunks, i.e. enough work items
+//                 to occupy every resident decode CTA; a block table much wider
+//                 than the sequences in it therefore costs nothing
+//   chunk_off[b]  exclusive prefix of chunks per sequence = first partial slot of b
 //   items[]       one record per chunk, in sequence order.  (Putting all short
 //                 last chunks at the end of the list was measured slower: equal
 //                 items make every CTA start and drain its copy pipeline at the
 //                 same moments.)
-//   hdr           chunk total, status, and the zeroed work counter
+//   hdr           chunk total, status, chosen base, and the zeroed work counter
 __global__ void __launch_bounds__(kPlanThreads) gqa_plan_kernel(const DecodeParams p) {
     __shared__ int s_warp[kPlanThreads / 32];
+    __shared__ int s_cand[kNumAutoBases][kPlanThreads / 32];
+    __shared__ int s_base;
     pdl_launch_dependents();
     pdl_wait();
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int base_tokens = p.chunk_base;
+    if (base_tokens == 0) {
+        int cnt[kNumAutoBases];
+#pragma unroll
+        for (int i = 0; i < kNumAutoBases; ++i) cnt[i] = 0;
+        for (int b = tid; b < p.batch; b += kPlanThreads) {
+            const int len = clamp_len(p, b);
+#pragma unroll
+            for (int i = 0; i < kNumAutoBases; ++i) cnt[i] += chunks_for(len, 1024 >> i);
+        }
+#pragma unroll
+        for (int i = 0; i < kNumAutoBases; ++i) {
+            int x = cnt[i];
+#pragma unroll
+            for (int d = 16; d >= 1; d >>= 1) x += __shfl_xor_sync(0xffffffffu, x, d);
+            if (lane == 0) s_cand[i][warp] = x;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            int pick = 1024 >> (kNumAutoBases - 1);
+            bool found = false;
+#pragma unroll
+            for (int i = 0; i < kNumAutoBases; ++i) {
+                int x = s_cand[i][lane];
+#pragma unroll
+                for (int d = 16; d >= 1; d >>= 1) x += __shfl_xor_sync(0xffffffffu, x, d);
+                if (!found && x >= p.item_target) { pick = 1024 >> i; found = true; }
+            }
+            if (lane == 0) s_base = pick;
+        }
+        __syncthreads();
+        base_tokens = s_base;
+    }
     int run_n = 0;
     for (int base = 0; base < p.batch; base += kPlanThreads) {
         const int b = base + tid;
         const int len = b < p.batch ? clamp_len(p, b) : 0;
-        const int n = chunks_for(len, p.chunk_base);
+        const int n = chunks_for(len, base_tokens);
         int tot_n;
         const int incl_n = plan_block_scan(n, s_warp, tot_n);
         if (b < p.batch) {
             const int co = run_n + incl_n - n;
             p.chunk_off[b] = co;
-            const int ct = chunk_tokens_for(len, p.chunk_base);
+            const int ct = chunk_tokens_for(len, base_tokens);
             const int flag = n == 1 ? kSingleFlag : 0;
-            const int slot0 = b * p.slots_per_seq;
-            for (int c = 0; c < n && c < p.slots_per_seq; ++c) {
+            for (int c = 0; c < n; ++c) {
                 const long long t0 = (long long)c * ct;
                 const int t1 = (int)(t0 + ct < len ? t0 + ct : len);
                 if (co + c < p.cap_chunks)
-                    p.items[co + c] = make_int4(b, (slot0 + c) | flag, (int)t0, t1);
+                    p.items[co + c] = make_int4(b, (co + c) | flag, (int)t0, t1);
             }
         }
         run_n += tot_n;
@@ -73,6 +111,7 @@ __global__ void __launch_bounds__(kPlanThreads) gqa_plan_kernel(const DecodePara
         p.hdr[kHdrTotalChunks] = run_n;
         p.hdr[kHdrCounter] = 0;
         p.hdr[kHdrStatus] = run_n > p.cap_chunks ? 1 : 0;
+        p.hdr[kHdrChunkBase] = base_tokens;
     }
 }
 
@@ -98,9 +137,10 @@ __global__ void __launch_bounds__(kMergeWarps * 32) gqa_merge_kernel(const Decod
     int n_parts;
     size_t first_slot = 0;
     if (p.mode == kModePlanned) {
-        n_parts = chunks_for(clamp_len(p, b), p.chunk_base);
-        if (n_parts > p.slots_per_seq) n_parts = p.slots_per_seq;
-        first_slot = (size_t)b * p.slots_per_seq;
+        const int c0 = p.chunk_off[b];
+        n_parts = p.chunk_off[b + 1] - c0;
+        if (c0 + n_parts > p.cap_chunks) n_parts = p.cap_chunks > c0 ? p.cap_chunks - c0 : 0;
+        first_slot = (size_t)c0;
         if (n_parts == 1) return;
     } else {
         n_parts = p.splits;
@@ -191,10 +231,9 @@ __global__ void __launch_bounds__(kMergeWarps * 32) gqa_merge_kernel(const Decod
 
 // Planned-mode merge for short sequences (few chunks each): one WARP per
 // (sequence, query head), four pairs per CTA; lanes own float4 columns.  The
-// chunk count comes from the sequence's own length (one load), the partial
-// slots are at a fixed place per sequence, and four partial rows are fetched at
-// a time, so a sequence of up to four chunks costs two dependent memory round
-// trips.  Batches are folded with a running max.  head_dim % 4 == 0.
+// chunk count and first partial slot come from chunk_off (one round trip) and
+// four partial rows are fetched at a time, so a sequence of up to four chunks
+// costs two dependent memory round trips.  head_dim % 4 == 0.
 template <typename T>
 __global__ void __launch_bounds__(kMergeWarps * 32) gqa_merge_warp_kernel(const DecodeParams p) {
     pdl_launch_dependents();
@@ -204,8 +243,9 @@ __global__ void __launch_bounds__(kMergeWarps * 32) gqa_merge_warp_kernel(const 
     if (pair >= (long long)p.batch * p.q_heads) return;
     const int b = (int)(pair / p.q_heads), hq = (int)(pair - (long long)b * p.q_heads);
     const int D = p.head_dim;
-    int n = chunks_for(clamp_len(p, b), p.chunk_base);
-    if (n > p.slots_per_seq) n = p.slots_per_seq;
+    const int c0 = p.chunk_off[b];
+    int n = p.chunk_off[b + 1] - c0;
+    if (c0 + n > p.cap_chunks) n = p.cap_chunks > c0 ? p.cap_chunks - c0 : 0;
     if (n == 1) return;
     T* out = reinterpret_cast<T*>(p.out) + ((size_t)b * p.q_heads + hq) * D;
     const int col0 = lane * 4, col1 = (32 + lane) * 4;
@@ -223,44 +263,78 @@ __global__ void __launch_bounds__(kMergeWarps * 32) gqa_merge_warp_kernel(const 
         if (use1) store4(col1, 0.f, 0.f, 0.f, 0.f);
         return;
     }
-    const size_t slot0 = (size_t)b * p.slots_per_seq;
+    const size_t slot0 = (size_t)c0;
     const float2* ml = p.part_ml + slot0 * p.q_heads + hq;
     const float* acc = p.part_acc + (slot0 * p.q_heads + hq) * D;
     const size_t ml_step = p.q_heads, acc_step = (size_t)p.q_heads * D;
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 a0 = zero4, a1 = zero4;
-    float mx = -INFINITY, sum = 0.f;
-    for (int c0 = 0; c0 < n; c0 += 4) {
-        float2 v[4];
-        float4 x0[4], x1[4];
+    // first four partial rows in flight before anything depends on them
+    float2 v[4];
+    float4 x0[4], x1[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const bool live = c0 + j < n;
-            v[j] = live ? ml[(c0 + j) * ml_step] : make_float2(-INFINITY, 0.f);
-            const float* src = acc + (c0 + j) * acc_step;
-            x0[j] = live && use0 ? *reinterpret_cast<const float4*>(src + col0) : zero4;
-            x1[j] = live && use1 ? *reinterpret_cast<const float4*>(src + col1) : zero4;
+    for (int j = 0; j < 4; ++j) {
+        const bool live = j < n;
+        v[j] = live ? ml[j * ml_step] : make_float2(-INFINITY, 0.f);
+        const float* src = acc + j * acc_step;
+        x0[j] = live && use0 ? *reinterpret_cast<const float4*>(src + col0) : zero4;
+        x1[j] = live && use1 ? *reinterpret_cast<const float4*>(src + col1) : zero4;
+    }
+    // global max over chunks that hold tokens (chunks 4.. only exist for longer sequences)
+    float mx = -INFINITY;
+    for (int c = 4 + lane; c < n; c += 32) {
+        const float2 u = ml[c * ml_step];
+        if (u.y > 0.f) mx = fmaxf(mx, u.x);
+    }
+    if (n > 4) {
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (v[j].y > 0.f) mx = fmaxf(mx, v[j].x);
+    // Four interleaved running sums (chunks c = j mod 4), added 0+1+2+3 at the end: the
+    // same order of additions as the CTA-per-pair kernel, whose warp j folds those chunks,
+    // so the two merge kernels give identical bits.
+    float4 a0[4], a1[4];
+    float sum[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { a0[j] = zero4; a1[j] = zero4; sum[j] = 0.f; }
+    for (int cb = 0; cb < n; cb += 4) {
+        if (cb > 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const bool live = cb + j < n;
+                v[j] = live ? ml[(cb + j) * ml_step] : make_float2(-INFINITY, 0.f);
+                const float* src = acc + (cb + j) * acc_step;
+                x0[j] = live && use0 ? *reinterpret_cast<const float4*>(src + col0) : zero4;
+                x1[j] = live && use1 ? *reinterpret_cast<const float4*>(src + col1) : zero4;
+            }
         }
-        float bm = mx;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            if (v[j].y > 0.f) bm = fmaxf(bm, v[j].x);
-        const float r = sum > 0.f ? fast_exp2(mx - bm) : 0.f;
-        sum *= r;
-        a0.x *= r; a0.y *= r; a0.z *= r; a0.w *= r;
-        a1.x *= r; a1.y *= r; a1.z *= r; a1.w *= r;
-        mx = bm;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const float wgt = v[j].y > 0.f ? fast_exp2(v[j].x - mx) : 0.f;
-            sum += wgt * v[j].y;
-            a0.x += wgt * x0[j].x; a0.y += wgt * x0[j].y; a0.z += wgt * x0[j].z; a0.w += wgt * x0[j].w;
-            a1.x += wgt * x1[j].x; a1.y += wgt * x1[j].y; a1.z += wgt * x1[j].z; a1.w += wgt * x1[j].w;
+            if (v[j].y > 0.f) {
+                const float wgt = fast_exp2(v[j].x - mx);
+                sum[j] += wgt * v[j].y;
+                a0[j].x += wgt * x0[j].x; a0[j].y += wgt * x0[j].y;
+                a0[j].z += wgt * x0[j].z; a0[j].w += wgt * x0[j].w;
+                a1[j].x += wgt * x1[j].x; a1[j].y += wgt * x1[j].y;
+                a1[j].z += wgt * x1[j].z; a1[j].w += wgt * x1[j].w;
+            }
         }
     }
-    const float inv = sum > 0.f ? 1.f / sum : 0.f;
-    if (use0) store4(col0, a0.x * inv, a0.y * inv, a0.z * inv, a0.w * inv);
-    if (use1) store4(col1, a1.x * inv, a1.y * inv, a1.z * inv, a1.w * inv);
+    auto fold = [](float s0, float s1, float s2, float s3) { return ((0.f + s0) + s1 + s2) + s3; };
+    const float tot = fold(sum[0], sum[1], sum[2], sum[3]);
+    const float inv = tot > 0.f ? 1.f / tot : 0.f;
+    if (use0)
+        store4(col0, fold(a0[0].x, a0[1].x, a0[2].x, a0[3].x) * inv,
+               fold(a0[0].y, a0[1].y, a0[2].y, a0[3].y) * inv,
+               fold(a0[0].z, a0[1].z, a0[2].z, a0[3].z) * inv,
+               fold(a0[0].w, a0[1].w, a0[2].w, a0[3].w) * inv);
+    if (use1)
+        store4(col1, fold(a1[0].x, a1[1].x, a1[2].x, a1[3].x) * inv,
+               fold(a1[0].y, a1[1].y, a1[2].y, a1[3].y) * inv,
+               fold(a1[0].z, a1[1].z, a1[2].z, a1[3].z) * inv,
+               fold(a1[0].w, a1[1].w, a1[2].w, a1[3].w) * inv);
 }
 
 }  // namespace gqa_b200

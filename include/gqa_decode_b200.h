@@ -63,20 +63,26 @@ extern "C" {
  *   word 0  work-item counter of the last launch
  *   word 1  number of (sequence, chunk) pairs the last plan produced
  *   word 2  device status: 0 ok, 1 = plan overflowed the workspace (cannot
- *           happen when it is sized by gqa_b200_workspace_bytes)            */
+ *           happen when it is sized by gqa_b200_workspace_bytes)
+ *   word 3  base chunk length the last plan used                            */
 #define GQA_B200_HDR_COUNTER 0
 #define GQA_B200_HDR_TOTAL_CHUNKS 1
 #define GQA_B200_HDR_STATUS 2
+#define GQA_B200_HDR_CHUNK_BASE 3
 
 GQA_B200_API int gqa_b200_abi_version(void);
 
 /* Text for a status code returned by any entry point (static storage). */
 GQA_B200_API const char* gqa_b200_strerror(int code);
 
-/* Base KV-chunk length (tokens) that chunk_tokens = 0 stands for.  Chosen from
- * the static shape and the B200 SM count alone, never from context_lens: the
- * largest of 1024 .. 64 that still cuts a full block table into about one work
- * item per resident CTA. */
+/* chunk_tokens = 0 leaves the base KV-chunk length to the plan kernel, which
+ * picks it ON THE DEVICE from the batch's actual context_lens (never read by
+ * the host): the largest of 1024, 512, 256, 128, 64 that still yields about one
+ * work item per resident decode CTA, so a small batch is cut finely enough to
+ * occupy every SM, a large one pays little per-chunk overhead, and a block
+ * table much wider than the sequences in it costs nothing.  The choice is
+ * stored in workspace header word GQA_B200_HDR_CHUNK_BASE.  This function
+ * previews the rule on the host for sequences that fill their table. */
 GQA_B200_API int gqa_b200_auto_chunk_tokens(int batch, int q_heads, int kv_heads, int block_size,
                                             int max_pages);
 

@@ -296,3 +296,60 @@ def test_kv_append_skips_out_of_range_positions():
     pos = torch.tensor([-1, 16 * table.shape[1]], dtype=torch.int32, device=DEV)
     attn.kv_append(key, key, dk, dv, table.to(DEV), pos)
     assert torch.equal(dk.cpu(), k) and torch.equal(dv.cpu(), v)
+
+
+# --------------------------------------------------------------------------- randomized shapes
+def test_randomized_shapes_against_oracle():
+    """Seeded sweep over dtypes, head layouts, head sizes, page sizes, chunk lengths and
+    ragged batches (with empty and one-token sequences mixed in)."""
+    rng = torch.Generator().manual_seed(1234)
+
+    def pick(options):
+        return options[int(torch.randint(len(options), (1,), generator=rng))]
+
+    for case in range(40):
+        dtype = pick([torch.float32, torch.float16, torch.bfloat16])
+        hkv = pick([1, 2, 3, 4, 8])
+        group = pick([1, 2, 4, 5, 7, 8, 16, 20])
+        d = pick([64, 128, 128, 128, 256, 32, 80, 100])
+        bs = pick([1, 4, 8, 16, 16, 32, 64, 128, 12])
+        batch = pick([1, 2, 5, 17])
+        top = pick([1, 40, 300, 1500])
+        lengths = torch.randint(0, top + 1, (batch,), generator=rng).tolist()
+        if case % 4 == 0:
+            lengths[0] = 0
+        chunk = pick([0, 0, 16, 64, 512])
+        kernel = pick(["auto", "auto", "simt"])
+        q, k, v, table, lens = _make_case(lengths, hkv * group, hkv, d, bs, dtype, seed=case)
+        args = _cuda(q, k, v, table, lens)
+        got = attn.gqa_decode(*args, chunk_tokens=chunk, kernel=kernel)
+        _assert_close(got, _oracle(*args), dtype,
+                      f"case {case}: {dtype} Hkv={hkv} G={group} D={d} bs={bs} L={lengths} "
+                      f"chunk={chunk} {kernel}")
+
+
+# --------------------------------------------------------------------------- stream capture
+def test_decode_can_be_captured_in_a_cuda_graph_and_replayed():
+    """No allocation, no host read of the lengths, no synchronisation inside the call: the
+    three launches can be recorded once and replayed on new contents of the same buffers."""
+    q, k, v, table, lens = _make_case([900, 40, 2500, 0, 64], 32, 8, 128, 16, torch.bfloat16, seed=21)
+    dq, dk, dv, dt, dl = _cuda(q, k, v, table, lens)
+    out = torch.empty_like(dq)
+    ws = torch.empty(attn.workspace_bytes(5, 32, 8, 128, 16, table.shape[1]), dtype=torch.uint8,
+                     device=DEV)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        attn.gqa_decode(dq, dk, dv, dt, dl, out=out, workspace=ws)     # warm-up outside capture
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        attn.gqa_decode(dq, dk, dv, dt, dl, out=out, workspace=ws)
+    graph.replay()
+    torch.cuda.synchronize()
+    _assert_close(out, _oracle(dq, dk, dv, dt, dl), torch.bfloat16, "first replay")
+    # new query, shorter/longer lengths within the same table, same buffers
+    dq.copy_(torch.randn_like(dq))
+    dl.copy_(torch.tensor([17, 33, 1200, 0, 5], dtype=torch.int32))   # within each row's pages
+    graph.replay()
+    torch.cuda.synchronize()
+    _assert_close(out, _oracle(dq, dk, dv, dt, dl), torch.bfloat16, "second replay")
