@@ -88,6 +88,24 @@ def pool_blocks_for(w: DecodeWorkload, lens: torch.Tensor) -> int:
     return max(1, math.ceil(w.pool_factor * need))
 
 
+def _draw_tensors(w: DecodeWorkload, lens: torch.Tensor, gen: torch.Generator, seed: int, device,
+                  kv_on_device: bool):
+    """q, K, V and the page table for given lengths, drawn in that order from ``gen``."""
+    q = torch.randn(w.batch, w.q_heads, w.head_dim, generator=gen, dtype=torch.float32)
+    pool = pool_blocks_for(w, lens)
+    shape = (pool, w.block_size, w.kv_heads, w.head_dim)
+    if kv_on_device:
+        dgen = torch.Generator(device=device).manual_seed(seed)
+        k = torch.empty(shape, dtype=w.dtype, device=device).normal_(generator=dgen)
+        v = torch.empty(shape, dtype=w.dtype, device=device).normal_(generator=dgen)
+    else:
+        k = torch.randn(shape, generator=gen, dtype=torch.float32).to(w.dtype).to(device)
+        v = torch.randn(shape, generator=gen, dtype=torch.float32).to(w.dtype).to(device)
+    table = build_block_table(lens, w.block_size, pool, gen)
+    return (q.to(device=device, dtype=w.dtype).contiguous(), k.contiguous(), v.contiguous(),
+            table.to(device).contiguous(), lens.to(device))
+
+
 def make_workload(w: DecodeWorkload | str, *, seed: int = 42, device="cpu",
                   kv_on_device: bool = False):
     """Returns (q, k_cache, v_cache, block_table, context_lens) for a workload.
@@ -102,19 +120,20 @@ def make_workload(w: DecodeWorkload | str, *, seed: int = 42, device="cpu",
         w = WORKLOADS[w]
     gen = torch.Generator(device="cpu").manual_seed(seed)
     lens = draw_lengths(w, gen)
-    q = torch.randn(w.batch, w.q_heads, w.head_dim, generator=gen, dtype=torch.float32)
-    pool = pool_blocks_for(w, lens)
-    shape = (pool, w.block_size, w.kv_heads, w.head_dim)
-    if kv_on_device:
-        dgen = torch.Generator(device=device).manual_seed(seed)
-        k = torch.empty(shape, dtype=w.dtype, device=device).normal_(generator=dgen)
-        v = torch.empty(shape, dtype=w.dtype, device=device).normal_(generator=dgen)
-    else:
-        k = torch.randn(shape, generator=gen, dtype=torch.float32).to(w.dtype).to(device)
-        v = torch.randn(shape, generator=gen, dtype=torch.float32).to(w.dtype).to(device)
-    table = build_block_table(lens, w.block_size, pool, gen)
-    return (q.to(device=device, dtype=w.dtype).contiguous(), k.contiguous(), v.contiguous(),
-            table.to(device).contiguous(), lens.to(device))
+    return _draw_tensors(w, lens, gen, seed, device, kv_on_device)
+
+
+def make_workload_for_lengths(w: DecodeWorkload | str, lens: torch.Tensor, *, seed: int = 42,
+                              device="cpu", kv_on_device: bool = False):
+    """Like ``make_workload`` but for given context lengths (e.g. one rank's share of a batch):
+    batch = len(lens), a private page pool of ``pool_factor`` x the pages those lengths need.
+    Returns (the resized workload, the five tensors)."""
+    if isinstance(w, str):
+        w = WORKLOADS[w]
+    lens = lens.to(torch.int32).cpu()
+    w = replace(w, batch=int(lens.numel()), fixed_pool_blocks=0)
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    return w, _draw_tensors(w, lens, gen, seed, device, kv_on_device)
 
 
 def scaled(w: DecodeWorkload | str, **changes) -> DecodeWorkload:

@@ -56,6 +56,9 @@ def parse_args():
                    help="target CPU time of the cpu_baseline sample")
     p.add_argument("--spinup-seconds", type=float, default=0.3,
                    help="extra untimed warm-up so the SM clock is out of idle")
+    p.add_argument("--scaling", choices=["weak", "strong"], default="weak",
+                   help="weak: every GPU gets its own batch of the workload (default); strong: "
+                        "ONE batch of the workload is sharded over the GPUs (longest-first)")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-cold-cache", action="store_true")
     return p.parse_args()
@@ -263,8 +266,20 @@ def run_b200(args):
         torch.cuda.synchronize()
 
     w = synth.WORKLOADS[args.workload]
-    q, k, v, table, lens = synth.make_workload(w, seed=args.seed + rank, device=dev,
-                                               kv_on_device=True)
+    imbalance = None
+    if args.scaling == "strong" and world > 1:
+        # one global batch; this rank owns the sequences the longest-first assignment gives
+        # it, in a page pool of its own with its own block table -- no data-path collective
+        from attention_b200 import sharding
+        all_lens = synth.draw_lengths(w, torch.Generator().manual_seed(args.seed))
+        shards = sharding.lpt_assign(all_lens.tolist(), world)
+        imbalance = sharding.load_imbalance(all_lens.tolist(), shards)
+        mine = all_lens[torch.as_tensor(shards[rank], dtype=torch.int64)]
+        w, (q, k, v, table, lens) = synth.make_workload_for_lengths(
+            w, mine, seed=args.seed + rank, device=dev, kv_on_device=True)
+    else:
+        q, k, v, table, lens = synth.make_workload(w, seed=args.seed + rank, device=dev,
+                                                   kv_on_device=True)
     my_bytes = workload_bytes(w, lens)
     kw = dict(kernel=args.kernel, chunk_tokens=args.chunk_tokens)
     K, W = args.steps, max(args.warmup, 3)
@@ -408,9 +423,11 @@ def run_b200(args):
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms_total / K, "us_per_call": ms_total / K * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "higher_is_better": True,
+        "scaling": args.scaling if world > 1 else "weak", "vs_baseline": None,
         "dtype": DTYPE_NAME[w.dtype], "data": "synthetic",
-        "config": config_of(w, {
+        "config": config_of(synth.WORKLOADS[args.workload], {
+            "lpt_load_imbalance": imbalance,
             "kernel": args.kernel, "chunk_tokens": args.chunk_tokens, "seed": args.seed,
             "l2": f"inputs {my_bytes / 1e6:.0f} MB per GPU, larger than the 126 MB L2; no flush",
             "bytes_per_step_per_gpu": my_bytes}),
