@@ -1,12 +1,12 @@
 """B200-native paged grouped-query decode attention (drop-in for the reference's
 ``attention.gqa_decode`` path)."""
 
-from .core import (gqa_decode, gqa_decode_auto, gqa_decode_split, is_cuda_extension_loaded,
-                   kv_append, workspace_bytes)
+from .core import (gqa_decode, gqa_decode_auto, gqa_decode_split, gqa_prefill,
+                   is_cuda_extension_loaded, kv_append, workspace_bytes)
 from .validation import validate_paged_metadata
 
 __all__ = [
-    "gqa_decode", "gqa_decode_split", "gqa_decode_auto", "kv_append",
+    "gqa_decode", "gqa_decode_split", "gqa_decode_auto", "gqa_prefill", "kv_append",
     "is_cuda_extension_loaded", "validate_paged_metadata", "workspace_bytes",
 ]
 __version__ = "0.1.0"

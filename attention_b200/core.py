@@ -299,3 +299,52 @@ def kv_append(key, value, k_cache, v_cache, block_table, positions):
             key.size(1), key.size(2), k_cache.size(0), k_cache.size(1), block_table.size(1),
             _stream_handle(key.device))
     _raise_status(rc, "kv_append")
+
+
+def gqa_prefill(q, k, v, q_lens, kv_lens, *, causal=True, scale=None, backend="cuda", kernel="auto"):
+    """Dense ``[B,T,H,D]`` GQA prefill; causal queries align to the right of the valid KV.
+
+    Same contract as the reference's ``gqa_prefill`` (attention/core.py:66-77,
+    csrc/cuda/dense/gqa_prefill.cu:104-123): rows at or past ``q_lens[b]`` come back as zeros.
+    ``backend`` is ``"cuda"`` or ``"tensorcore"`` as in the reference; both run this library's
+    kernels (the tensor-core kernel is picked whenever the tensors allow it), ``"tensorcore"``
+    additionally insists on fp16/bf16 like the reference's Triton path.  ``kernel`` is a
+    tuning knob: ``"auto" | "simt" | "mma"``.
+    """
+    if backend not in ("cuda", "tensorcore"):
+        raise ValueError("backend must be cuda or tensorcore")
+    lib = _lib()
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    scale = float(scale)
+    for t in (q, k, v, q_lens, kv_lens):
+        _check(isinstance(t, torch.Tensor) and t.is_cuda and t.is_contiguous(),
+               "all inputs must be contiguous CUDA tensors")
+        _check(t.device == q.device, "all inputs must be on the same device")
+    _check(q.dim() == 4 and k.dim() == 4 and v.shape == k.shape, "q/k/v must be [B,T,H,D]")
+    _check(q.size(0) == k.size(0) and q.size(3) == k.size(3), "batch or head_dim mismatch")
+    _check(q.size(2) > 0 and k.size(2) > 0 and q.size(2) % k.size(2) == 0, "invalid head mapping")
+    _check(0 < q.size(3) <= 256, "head_dim must be in [1,256]")
+    _check(q.size(0) <= 65535 and q.size(1) <= 65535 and k.size(1) <= 2**31 - 1,
+           "dimensions exceed launch limits")
+    _check(q_lens.dim() == 1 and kv_lens.dim() == 1 and q_lens.size(0) == q.size(0)
+           and kv_lens.size(0) == q.size(0), "lengths must be [B]")
+    _check(q_lens.dtype == torch.int32 and kv_lens.dtype == torch.int32, "lengths must be int32")
+    _check(q.dtype == k.dtype == v.dtype, "dtype mismatch")
+    _check(q.dtype in _DTYPE_CODE, "unsupported dtype")
+    _check(math.isfinite(scale) and scale > 0, "scale must be positive and finite")
+    if backend == "tensorcore" and q.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("tensorcore backend requires matching fp16 or bf16")
+    if kernel not in ("auto", "simt", "mma"):
+        raise ValueError("kernel must be auto, simt or mma")
+    out = torch.empty_like(q)
+    if q.size(0) == 0 or q.size(1) == 0:
+        return out
+    with _on_device(q.device):
+        rc = lib.gqa_b200_prefill(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), q_lens.data_ptr(), kv_lens.data_ptr(),
+            out.data_ptr(), _DTYPE_CODE[q.dtype], q.size(0), q.size(1), k.size(1), q.size(2),
+            k.size(2), q.size(3), scale, 1 if causal else 0, _KERNEL_CODE[kernel],
+            _stream_handle(q.device))
+    _raise_status(rc, "gqa_prefill")
+    return out

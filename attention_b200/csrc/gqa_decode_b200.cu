@@ -13,6 +13,8 @@
 #include "gqa_decode_mma.cuh"
 #include "gqa_decode_simt.cuh"
 #include "gqa_plan_merge.cuh"
+#include "gqa_prefill_mma.cuh"
+#include "gqa_prefill_simt.cuh"
 #include "kv_append.cuh"
 
 using namespace gqa_b200;
@@ -619,6 +621,109 @@ int gqa_b200_decode_split(const void* q, const void* k_cache, const void* v_cach
     cudaError_t e = launch_decode(p, dtype, use_mma, 0, s);
     if (e != cudaSuccess) return (int)e;
     if (splits > 1) e = launch_merge(p, dtype, s);
+    return (int)e;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// dense prefill
+// ---------------------------------------------------------------------------
+namespace {
+
+template <typename T, int EPL, bool CONTIG>
+cudaError_t launch_prefill_simt(const PrefillParams& p, cudaStream_t stream) {
+    const int rows_per_cta = kPrefillRows * kPrefillWarps;
+    const dim3 grid((unsigned)((p.tq + rows_per_cta - 1) / rows_per_cta), (unsigned)p.q_heads,
+                    (unsigned)p.batch);
+    gqa_prefill_simt_kernel<T, EPL, CONTIG><<<grid, kPrefillWarps * 32, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_prefill_simt_for_dim(const PrefillParams& p, cudaStream_t stream) {
+    const int D = p.head_dim;
+    const bool contig = (D % 32 == 0) && aligned16(p.q) && aligned16(p.k) && aligned16(p.v) &&
+                        aligned16(p.out);
+    const int epl = (D + 31) / 32;
+    if (contig) {
+        switch (epl) {
+            case 1: return launch_prefill_simt<T, 1, true>(p, stream);
+            case 2: return launch_prefill_simt<T, 2, true>(p, stream);
+            case 4: return launch_prefill_simt<T, 4, true>(p, stream);
+            case 8: return launch_prefill_simt<T, 8, true>(p, stream);
+            default: break;
+        }
+    }
+    if (epl <= 1) return launch_prefill_simt<T, 1, false>(p, stream);
+    if (epl <= 2) return launch_prefill_simt<T, 2, false>(p, stream);
+    if (epl <= 4) return launch_prefill_simt<T, 4, false>(p, stream);
+    return launch_prefill_simt<T, 8, false>(p, stream);
+}
+
+template <typename T, int D>
+cudaError_t launch_prefill_mma(const PrefillParams& p, cudaStream_t stream) {
+    DeviceInfo* dev = nullptr;
+    cudaError_t e = device_info(&dev);
+    if (e != cudaSuccess) return e;
+    const size_t smem = PrefillGeom<D>::kSmemBytes;
+    int per_sm = 0;   // the first call also raises the kernel's dynamic shared-memory limit
+    e = resident_ctas(gqa_prefill_mma_kernel<T, D>, kPfWarps * 32, smem, dev->max_smem_optin, &per_sm);
+    if (e != cudaSuccess) return e;
+    const dim3 grid((unsigned)((p.tq + kPfBM - 1) / kPfBM), (unsigned)p.q_heads, (unsigned)p.batch);
+    gqa_prefill_mma_kernel<T, D><<<grid, kPfWarps * 32, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_prefill_t(const PrefillParams& p, bool use_mma, cudaStream_t stream) {
+    if (use_mma) {
+        if constexpr (sizeof(T) == 2) {
+            if (p.head_dim == 64) return launch_prefill_mma<T, 64>(p, stream);
+            return launch_prefill_mma<T, 128>(p, stream);
+        } else {
+            return cudaErrorInvalidValue;
+        }
+    }
+    return launch_prefill_simt_for_dim<T>(p, stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+int gqa_b200_prefill(const void* q, const void* k, const void* v, const int32_t* q_lens,
+                     const int32_t* kv_lens, void* out, int dtype, int batch, int tq, int tk,
+                     int q_heads, int kv_heads, int head_dim, float scale, int causal, int kernel,
+                     void* stream) {
+    if (dtype != GQA_B200_F32 && dtype != GQA_B200_F16 && dtype != GQA_B200_BF16)
+        return GQA_B200_ERR_DTYPE;
+    if (batch < 0 || tq < 0 || tk < 0) return GQA_B200_ERR_BATCH;
+    if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) return GQA_B200_ERR_HEADS;
+    if (head_dim <= 0 || head_dim > 256) return GQA_B200_ERR_HEAD_DIM;
+    if (!(std::isfinite(scale) && scale > 0.f)) return GQA_B200_ERR_SCALE;
+    if (batch > 65535 || q_heads > 65535) return GQA_B200_ERR_INT32_RANGE;
+    if (kernel != GQA_B200_KERNEL_AUTO && kernel != GQA_B200_KERNEL_SIMT &&
+        kernel != GQA_B200_KERNEL_MMA)
+        return GQA_B200_ERR_KERNEL;
+    if (batch == 0 || tq == 0) return GQA_B200_OK;
+    if (!q || !out || !q_lens || !kv_lens || (tk > 0 && (!k || !v))) return GQA_B200_ERR_NULL_POINTER;
+    PrefillParams p{};
+    p.q = q; p.k = k; p.v = v; p.out = out; p.q_lens = q_lens; p.kv_lens = kv_lens;
+    p.batch = batch; p.tq = tq; p.tk = tk; p.q_heads = q_heads; p.kv_heads = kv_heads;
+    p.group = q_heads / kv_heads; p.head_dim = head_dim; p.causal = causal ? 1 : 0;
+    p.scale_log2 = scale * kLog2e;
+    bool use_mma = dtype != GQA_B200_F32 && (head_dim == 64 || head_dim == 128) && aligned16(q) &&
+                   aligned16(k) && aligned16(v) && aligned16(out);
+    if (kernel == GQA_B200_KERNEL_MMA && !use_mma) return GQA_B200_ERR_KERNEL;
+    if (kernel == GQA_B200_KERNEL_SIMT) use_mma = false;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    switch (dtype) {
+        case GQA_B200_F32:  e = launch_prefill_t<float>(p, use_mma, s); break;
+        case GQA_B200_F16:  e = launch_prefill_t<__half>(p, use_mma, s); break;
+        default:            e = launch_prefill_t<__nv_bfloat16>(p, use_mma, s); break;
+    }
     return (int)e;
 }
 

@@ -192,6 +192,21 @@ GQA_B200_API int gqa_b200_decode_split(const void* q, const void* k_cache, const
                                        int max_pages, float scale, int splits, float* partials,
                                        void* stream);
 
+/* Dense (non-paged) GQA prefill.  Replaces gqa_prefill_cuda
+ * (csrc/cuda/dense/gqa_prefill.cu:104-141, kernels :19-100) and the reference's
+ * Triton "tensorcore" backend (attention/triton_prefill.py): q/out are
+ * [batch, tq, q_heads, head_dim], k/v [batch, tk, kv_heads, head_dim], q_lens /
+ * kv_lens int32 [batch].  Query row i of a sequence attends to keys
+ * 0 .. kv_len - q_len + i when `causal` (right-aligned causal mask,
+ * csrc/cuda/common/tile_utils.cuh:6-9), else to all kv_len keys; rows at or past
+ * q_len, and rows that see no key, are written as zeros.  One kernel launch, no
+ * scratch.  `kernel`: GQA_B200_KERNEL_AUTO / _SIMT / _MMA (fp16/bf16, head_dim
+ * 64 or 128, 16-byte aligned tensors). */
+GQA_B200_API int gqa_b200_prefill(const void* q, const void* k, const void* v,
+                                  const int32_t* q_lens, const int32_t* kv_lens, void* out,
+                                  int dtype, int batch, int tq, int tk, int q_heads, int kv_heads,
+                                  int head_dim, float scale, int causal, int kernel, void* stream);
+
 /* Write one new token per sequence into its page.  Replaces kv_append_cuda
  * (csrc/cuda/cache/kv_append.cu:29-56): key/value are [batch, kv_heads,
  * head_dim]; the row goes to block_table[b, positions[b] / block_size], slot

@@ -37,7 +37,7 @@ TOL = {torch.float32: 1e-4, torch.float16: 2e-3, torch.bfloat16: 1e-2}
 
 
 def full_cases():
-    return sorted(p.stem for p in GOLDEN_DIR.glob("full_*.npz"))
+    return sorted(p.stem for p in GOLDEN_DIR.glob("full_*.npz"))   # decode, inputs stored
 
 
 def seed_cases():
@@ -68,3 +68,17 @@ def load_seeded(name):
     inputs = synth.make_workload(w, seed=int(z["seed"]))
     assert digest(*inputs) == str(z["digest"]), "regenerated inputs differ from the fixture's"
     return inputs, from_np(z["out"], dn)
+
+
+def prefill_cases():
+    return sorted(p.stem for p in GOLDEN_DIR.glob("prefill_*.npz"))
+
+
+def load_prefill(name):
+    """-> (q, k, v, q_lens, kv_lens, causal, scale_or_None, reference_out)"""
+    z = np.load(GOLDEN_DIR / f"{name}.npz")
+    dn = str(z["dtype"])
+    scale = float(z["scale"])
+    return (from_np(z["q"], dn), from_np(z["k"], dn), from_np(z["v"], dn),
+            torch.from_numpy(z["q_lens"].copy()), torch.from_numpy(z["kv_lens"].copy()),
+            bool(int(z["causal"])), None if scale < 0 else scale, from_np(z["out"], dn))

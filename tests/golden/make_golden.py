@@ -83,5 +83,38 @@ def main(ref_root: str) -> None:
         print(name, tuple(out.shape), lens.tolist()[:8])
 
 
+def prefill_cases(ref_root: str) -> None:
+    """Dense prefill fixtures from the reference's ``reference_gqa_prefill``
+    (attention/reference/gqa.py:47-64): inputs stored in full."""
+    sys.path.insert(0, ref_root)
+    from attention.reference.gqa import reference_gqa_prefill
+
+    cases = [
+        # name, B, Tq, Tk, Hq, Hkv, D, dtype, q_lens, kv_lens, causal, scale, seed
+        ("prefill_f32_causal_d32", 3, 9, 12, 6, 2, 32, torch.float32, [9, 4, 0], [12, 4, 7], True, None, 1),
+        ("prefill_bf16_causal_d128", 2, 40, 40, 8, 2, 128, torch.bfloat16, [40, 17], [40, 17], True, None, 2),
+        ("prefill_f16_noncausal_d64", 2, 20, 33, 4, 4, 64, torch.float16, [20, 5], [33, 30], False, 0.2, 3),
+        ("prefill_bf16_qlonger_d128", 2, 70, 50, 7, 1, 128, torch.bfloat16, [70, 33], [50, 40], True, None, 4),
+        ("prefill_f16_chunked_d128", 2, 16, 200, 8, 2, 128, torch.float16, [16, 9], [200, 137], True, None, 5),
+        ("prefill_f32_mqa_d80", 2, 11, 11, 5, 1, 80, torch.float32, [11, 6], [11, 6], True, None, 6),
+    ]
+    for name, b, tq, tk, hq, hkv, d, dtype, ql, kl, causal, scale, seed in cases:
+        gen = torch.Generator().manual_seed(seed)
+        q = torch.randn(b, tq, hq, d, generator=gen).to(dtype)
+        k = torch.randn(b, tk, hkv, d, generator=gen).to(dtype)
+        v = torch.randn(b, tk, hkv, d, generator=gen).to(dtype)
+        q_lens = torch.tensor(ql, dtype=torch.int32)
+        kv_lens = torch.tensor(kl, dtype=torch.int32)
+        out = reference_gqa_prefill(q, k, v, q_lens, kv_lens, causal=causal, scale=scale)
+        np.savez_compressed(
+            HERE / f"{name}.npz", q=to_np(q), k=to_np(k), v=to_np(v), q_lens=to_np(q_lens),
+            kv_lens=to_np(kv_lens), out=to_np(out), dtype=str(dtype).replace("torch.", ""),
+            causal=np.int64(1 if causal else 0), scale=np.float64(-1.0 if scale is None else scale))
+        print(name, tuple(out.shape))
+
+
 if __name__ == "__main__":
+    prefill_cases(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if "--prefill-only" in sys.argv:
+        sys.exit(0)
     main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -1,0 +1,125 @@
+"""Dense GQA prefill: the oracle against the reference's outputs (CPU), and the CUDA
+kernels (through the C ABI) against the oracle (GPU)."""
+
+import pytest
+import torch
+
+from conftest import TOL, load_prefill, prefill_cases
+from oracle import gqa_oracle
+
+import attention_b200 as attn
+
+DEV = "cuda"
+
+
+def _close(got, want, dtype, what=""):
+    tol = TOL[dtype]
+    torch.testing.assert_close(got.float().cpu(), want.float().cpu(), atol=tol, rtol=tol,
+                               msg=lambda m: f"{what}: {m}")
+
+
+# --------------------------------------------------------------------------- CPU: oracle pin
+@pytest.mark.parametrize("name", prefill_cases())
+def test_prefill_oracle_matches_reference(name):
+    q, k, v, ql, kl, causal, scale, want = load_prefill(name)
+    got = gqa_oracle.reference_gqa_prefill(q, k, v, ql, kl, causal=causal, scale=scale)
+    assert got.shape == q.shape and got.dtype == q.dtype
+    _close(got, want, q.dtype, name)
+
+
+def test_prefill_oracle_padding_rows_are_zero():
+    q, k, v, ql, kl, causal, scale, _ = load_prefill("prefill_bf16_qlonger_d128")
+    out = gqa_oracle.reference_gqa_prefill(q, k, v, ql, kl, causal=causal, scale=scale)
+    # sequence 0: 70 queries over 50 keys, right aligned: the first 20 rows see nothing
+    assert torch.count_nonzero(out[0, :20]) == 0 and torch.count_nonzero(out[0, 20]) > 0
+    assert torch.count_nonzero(out[1, int(ql[1]):]) == 0
+
+
+def test_prefill_front_door_rejects_cpu_tensors():
+    q, k, v, ql, kl, causal, scale, _ = load_prefill("prefill_f32_causal_d32")
+    with pytest.raises(RuntimeError, match="CUDA"):
+        attn.gqa_prefill(q, k, v, ql, kl)
+    with pytest.raises(ValueError):
+        attn.gqa_prefill(q, k, v, ql, kl, backend="triton")
+
+
+# --------------------------------------------------------------------------- GPU parity
+def _case(b, tq, tk, hq, hkv, d, dtype, q_lens, kv_lens, seed=0):
+    gen = torch.Generator().manual_seed(seed)
+    q = torch.randn(b, tq, hq, d, generator=gen).to(dtype)
+    k = torch.randn(b, tk, hkv, d, generator=gen).to(dtype)
+    v = torch.randn(b, tk, hkv, d, generator=gen).to(dtype)
+    return (q.to(DEV), k.to(DEV), v.to(DEV), torch.tensor(q_lens, dtype=torch.int32, device=DEV),
+            torch.tensor(kv_lens, dtype=torch.int32, device=DEV))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kernel", ["auto", "simt"])
+@pytest.mark.parametrize("name", prefill_cases())
+def test_prefill_golden(name, kernel):
+    q, k, v, ql, kl, causal, scale, want = load_prefill(name)
+    got = attn.gqa_prefill(q.to(DEV), k.to(DEV), v.to(DEV), ql.to(DEV), kl.to(DEV), causal=causal,
+                           scale=scale, kernel=kernel)
+    _close(got, want, q.dtype, f"{name} {kernel}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("causal", [True, False])
+def test_prefill_ragged_batches(dtype, causal):
+    """Lengths around the 64-row / 64-key tile edges, q shorter, equal and longer than kv,
+    empty sequences, chunked prefill (few queries over a long prefix)."""
+    q_lens = [0, 1, 63, 64, 65, 130, 200, 16, 7, 200]
+    kv_lens = [5, 1, 63, 64, 65, 300, 150, 300, 0, 200]
+    args = _case(10, 200, 300, 8, 2, 128, dtype, q_lens, kv_lens, seed=3)
+    want = gqa_oracle.reference_gqa_prefill(*args, causal=causal)
+    for kernel in ("auto", "simt"):
+        got = attn.gqa_prefill(*args, causal=causal, kernel=kernel)
+        _close(got, want, dtype, f"{dtype} causal={causal} {kernel}")
+        assert torch.count_nonzero(got[0]) == 0 and torch.count_nonzero(got[8]) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("hq,hkv,d", [(4, 4, 128), (8, 1, 128), (28, 4, 128), (6, 2, 64), (5, 1, 64),
+                                       (8, 2, 256), (4, 2, 96), (3, 3, 40)])
+def test_prefill_head_layouts_and_sizes(hq, hkv, d):
+    args = _case(2, 150, 150, hq, hkv, d, torch.bfloat16, [150, 77], [150, 77], seed=hq + d)
+    want = gqa_oracle.reference_gqa_prefill(*args)
+    _close(attn.gqa_prefill(*args), want, torch.bfloat16, f"{hq}/{hkv} D={d}")
+    _close(attn.gqa_prefill(*args, backend="tensorcore"), want, torch.bfloat16)
+
+
+@pytest.mark.gpu
+def test_prefill_long_sequence_and_scale():
+    args = _case(1, 2048, 2048, 8, 2, 128, torch.bfloat16, [2048], [2048], seed=9)
+    want = gqa_oracle.reference_gqa_prefill(*args, scale=0.05)
+    _close(attn.gqa_prefill(*args, scale=0.05), want, torch.bfloat16, "2k causal")
+    args = _case(2, 33, 4096, 8, 2, 128, torch.float16, [33, 20], [4096, 3000], seed=10)
+    want = gqa_oracle.reference_gqa_prefill(*args)
+    _close(attn.gqa_prefill(*args), want, torch.float16, "chunked over 4k prefix")
+
+
+@pytest.mark.gpu
+def test_prefill_argument_checks():
+    q, k, v, ql, kl = _case(2, 8, 8, 4, 2, 64, torch.float16, [8, 3], [8, 3])
+    bad = [
+        (dict(q=q[0]), r"\[B,T,H,D\]"),
+        (dict(v=v[:, :4].contiguous()), r"\[B,T,H,D\]"),
+        (dict(k=k[:1], v=v[:1]), "batch or head_dim"),
+        (dict(q=q[:, :, :3].contiguous()), "head mapping"),
+        (dict(ql=ql[:1]), r"lengths must be \[B\]"),
+        (dict(ql=ql.long()), "int32"),
+        (dict(q=q.float()), "dtype mismatch"),
+        (dict(q=q.double(), k=k.double(), v=v.double()), "unsupported dtype"),
+        (dict(scale=0.0), "scale"),
+        (dict(q=q.transpose(1, 2)), "contiguous"),
+    ]
+    for change, pattern in bad:
+        a = dict(q=q, k=k, v=v, ql=ql, kl=kl, scale=None)
+        a.update(change)
+        with pytest.raises(RuntimeError, match=pattern):
+            attn.gqa_prefill(a["q"], a["k"], a["v"], a["ql"], a["kl"], scale=a["scale"])
+    with pytest.raises(ValueError, match="tensorcore"):
+        attn.gqa_prefill(q.float(), k.float(), v.float(), ql, kl, backend="tensorcore")
+    empty = attn.gqa_prefill(q[:0], k[:0], v[:0], ql[:0], kl[:0])
+    assert empty.shape == (0, 8, 4, 64)
