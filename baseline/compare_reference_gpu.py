@@ -67,12 +67,45 @@ def time_call(fn, min_seconds=0.2, reps=20):
     return statistics.median(samples)
 
 
+def compare_prefill(ref):
+    """Dense prefill: this library vs the reference's CUDA kernels and its Triton backend."""
+    for b, t in ((8, 1024), (4, 4096)):
+        gen = torch.Generator(device="cuda").manual_seed(42)
+        q = torch.empty(b, t, 32, 128, device="cuda", dtype=torch.bfloat16).normal_(generator=gen)
+        k = torch.empty(b, t, 8, 128, device="cuda", dtype=torch.bfloat16).normal_(generator=gen)
+        v = torch.empty(b, t, 8, 128, device="cuda", dtype=torch.bfloat16).normal_(generator=gen)
+        lens = torch.full((b,), t, dtype=torch.int32, device="cuda")
+        flops = 4.0 * b * 32 * 128 * t * t * 0.5
+        mine = ours.gqa_prefill(q, k, v, lens, lens)
+        row = {"workload": f"prefill B{b} T{t} 32/8 D128 bf16 causal"}
+        legs = {
+            "b200": lambda: ours.gqa_prefill(q, k, v, lens, lens),
+            "ref_cuda": lambda: ref.gqa_prefill(q, k, v, lens, lens),
+            "ref_triton_tensorcore": lambda: ref.gqa_prefill(q, k, v, lens, lens, backend="tensorcore"),
+        }
+        for leg, fn in legs.items():
+            try:
+                out = fn()
+                torch.cuda.synchronize()
+                close = torch.allclose(out.float(), mine.float(), atol=2e-2, rtol=2e-2)
+                us = time_call(fn, reps=10 if leg == "b200" else 2)
+                row[leg] = {"us": round(us, 1), "TFLOPs": round(flops / us / 1e6, 1),
+                            "max_abs_diff_vs_b200": (out.float() - mine.float()).abs().max().item(),
+                            "close": bool(close)}
+            except Exception as exc:   # noqa: BLE001
+                row[leg] = {"error": str(exc)[:200]}
+        print(json.dumps(row), flush=True)
+
+
 def main():
-    names = sys.argv[1:] or list(synth.WORKLOADS)
+    names = [a for a in sys.argv[1:] if a != "prefill"] or (
+        [] if "prefill" in sys.argv[1:] else list(synth.WORKLOADS))
     ref, why = load_reference()
     if ref is None:
         print(json.dumps({"unavailable": why}))
         return
+    if "prefill" in sys.argv[1:] or not sys.argv[1:]:
+        compare_prefill(ref)
     for name in names:
         w = synth.WORKLOADS[name]
         q, k, v, table, lens = synth.make_workload(w, seed=42, device="cuda", kv_on_device=True)
