@@ -25,6 +25,7 @@ SIGNATURES = {
     "gqa_b200_decode_split": (c_int, [_P] * 6 + [c_int] * 5 + [c_int64, c_int, c_int, c_float,
                                                                 c_int, _P, _P]),
     "gqa_b200_prefill": (c_int, [_P] * 6 + [c_int] * 7 + [c_float, c_int, c_int, _P]),
+    "gqa_b200_prefill_tc_status": (c_int, [c_int]),
     "gqa_b200_kv_append": (c_int, [_P] * 6 + [c_int] * 4 + [c_int64, c_int, c_int, _P]),
 }
 

@@ -19,7 +19,7 @@ import torch
 from . import _cabi
 
 _DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
-_KERNEL_CODE = {"auto": 0, "simt": 1, "mma": 2}
+_KERNEL_CODE = {"auto": 0, "simt": 1, "mma": 2, "tcgen05": 4}
 
 # (device index, stream handle) -> uint8 scratch tensor, grown on demand
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
@@ -188,7 +188,7 @@ def gqa_decode(q, k_cache, v_cache, block_table, context_lens, *, scale=None, ou
     if not _decode_inputs_ok(q, k_cache, v_cache, block_table, context_lens, scale):
         _validate_decode(q, k_cache, v_cache, block_table, context_lens, scale)
         raise RuntimeError("invalid gqa_decode arguments")   # not reached: the line above raises
-    if kernel not in _KERNEL_CODE:
+    if kernel not in ("auto", "simt", "mma"):
         raise ValueError("kernel must be auto, simt or mma")
     if out is None:
         out = torch.empty_like(q)
@@ -309,7 +309,7 @@ def gqa_prefill(q, k, v, q_lens, kv_lens, *, causal=True, scale=None, backend="c
     ``backend`` is ``"cuda"`` or ``"tensorcore"`` as in the reference; both run this library's
     kernels (the tensor-core kernel is picked whenever the tensors allow it), ``"tensorcore"``
     additionally insists on fp16/bf16 like the reference's Triton path.  ``kernel`` is a
-    tuning knob: ``"auto" | "simt" | "mma"``.
+    tuning knob: ``"auto" | "simt" | "mma" | "tcgen05"``.
     """
     if backend not in ("cuda", "tensorcore"):
         raise ValueError("backend must be cuda or tensorcore")
@@ -335,8 +335,8 @@ def gqa_prefill(q, k, v, q_lens, kv_lens, *, causal=True, scale=None, backend="c
     _check(math.isfinite(scale) and scale > 0, "scale must be positive and finite")
     if backend == "tensorcore" and q.dtype not in (torch.float16, torch.bfloat16):
         raise ValueError("tensorcore backend requires matching fp16 or bf16")
-    if kernel not in ("auto", "simt", "mma"):
-        raise ValueError("kernel must be auto, simt or mma")
+    if kernel not in ("auto", "simt", "mma", "tcgen05"):
+        raise ValueError("kernel must be auto, simt, mma or tcgen05")
     out = torch.empty_like(q)
     if q.size(0) == 0 or q.size(1) == 0:
         return out

@@ -15,6 +15,7 @@
 #include "gqa_plan_merge.cuh"
 #include "gqa_prefill_mma.cuh"
 #include "gqa_prefill_simt.cuh"
+#include "gqa_prefill_tc.cuh"
 #include "kv_append.cuh"
 
 using namespace gqa_b200;
@@ -23,6 +24,7 @@ namespace {
 
 constexpr int kTableEntriesBudget = 2048;   // page ids staged in shared memory per segment
 constexpr int kMaxDevices = 64;
+constexpr bool kPrefillAutoPicksTcgen05 = true;    // KERNEL_AUTO prefers the tcgen05 prefill kernel
 constexpr int kWarpMergeMinPairs = 1024;    // fewer (sequence, head) pairs: CTA-per-pair merge
 
 struct DeviceInfo {
@@ -675,8 +677,53 @@ cudaError_t launch_prefill_mma(const PrefillParams& p, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
+// Status word of the tcgen05 prefill kernel: 0 ok, 2 = an mbarrier wait ran out, 3 = the
+// dynamic shared memory base was not 1024-byte aligned.  Read with gqa_b200_prefill_tc_status.
+static __device__ int g_prefill_tc_status;
+static int* g_prefill_tc_status_ptr[kMaxDevices];
+
+cudaError_t prefill_tc_status_address(int** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (!g_prefill_tc_status_ptr[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_prefill_tc_status);
+        if (e != cudaSuccess) return e;
+        g_prefill_tc_status_ptr[dev] = static_cast<int*>(ptr);
+    }
+    *out = g_prefill_tc_status_ptr[dev];
+    return cudaSuccess;
+}
+
+template <typename T, int D>
+cudaError_t launch_prefill_tc(const PrefillParams& p, cudaStream_t stream) {
+    DeviceInfo* dev = nullptr;
+    cudaError_t e = device_info(&dev);
+    if (e != cudaSuccess) return e;
+    const size_t smem = PrefillTcGeom<D>::kSmemBytes;
+    int per_sm = 0;
+    e = resident_ctas(gqa_prefill_tc_kernel<T, D>, kTcThreads, smem, dev->max_smem_optin, &per_sm);
+    if (e != cudaSuccess) return e;
+    int* status = nullptr;
+    e = prefill_tc_status_address(&status);
+    if (e != cudaSuccess) return e;
+    const dim3 grid((unsigned)((p.tq + kTcBM - 1) / kTcBM), (unsigned)p.q_heads, (unsigned)p.batch);
+    gqa_prefill_tc_kernel<T, D><<<grid, kTcThreads, smem, stream>>>(p, status);
+    return cudaGetLastError();
+}
+
 template <typename T>
-cudaError_t launch_prefill_t(const PrefillParams& p, bool use_mma, cudaStream_t stream) {
+cudaError_t launch_prefill_t(const PrefillParams& p, bool use_mma, bool use_tc, cudaStream_t stream) {
+    if (use_tc) {
+        if constexpr (sizeof(T) == 2) {
+            if (p.head_dim == 64) return launch_prefill_tc<T, 64>(p, stream);
+            return launch_prefill_tc<T, 128>(p, stream);
+        } else {
+            return cudaErrorInvalidValue;
+        }
+    }
     if (use_mma) {
         if constexpr (sizeof(T) == 2) {
             if (p.head_dim == 64) return launch_prefill_mma<T, 64>(p, stream);
@@ -704,7 +751,7 @@ int gqa_b200_prefill(const void* q, const void* k, const void* v, const int32_t*
     if (!(std::isfinite(scale) && scale > 0.f)) return GQA_B200_ERR_SCALE;
     if (batch > 65535 || q_heads > 65535) return GQA_B200_ERR_INT32_RANGE;
     if (kernel != GQA_B200_KERNEL_AUTO && kernel != GQA_B200_KERNEL_SIMT &&
-        kernel != GQA_B200_KERNEL_MMA)
+        kernel != GQA_B200_KERNEL_MMA && kernel != GQA_B200_KERNEL_TCGEN05)
         return GQA_B200_ERR_KERNEL;
     if (batch == 0 || tq == 0) return GQA_B200_OK;
     if (!q || !out || !q_lens || !kv_lens || (tk > 0 && (!k || !v))) return GQA_B200_ERR_NULL_POINTER;
@@ -715,16 +762,35 @@ int gqa_b200_prefill(const void* q, const void* k, const void* v, const int32_t*
     p.scale_log2 = scale * kLog2e;
     bool use_mma = dtype != GQA_B200_F32 && (head_dim == 64 || head_dim == 128) && aligned16(q) &&
                    aligned16(k) && aligned16(v) && aligned16(out);
-    if (kernel == GQA_B200_KERNEL_MMA && !use_mma) return GQA_B200_ERR_KERNEL;
+    if ((kernel == GQA_B200_KERNEL_MMA || kernel == GQA_B200_KERNEL_TCGEN05) && !use_mma)
+        return GQA_B200_ERR_KERNEL;
     if (kernel == GQA_B200_KERNEL_SIMT) use_mma = false;
+    // the tcgen05 kernel covers the same shapes as the mma.sync one
+    const bool use_tc = use_mma && (kernel == GQA_B200_KERNEL_TCGEN05 ||
+                                    (kernel == GQA_B200_KERNEL_AUTO && kPrefillAutoPicksTcgen05));
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e;
     switch (dtype) {
-        case GQA_B200_F32:  e = launch_prefill_t<float>(p, use_mma, s); break;
-        case GQA_B200_F16:  e = launch_prefill_t<__half>(p, use_mma, s); break;
-        default:            e = launch_prefill_t<__nv_bfloat16>(p, use_mma, s); break;
+        case GQA_B200_F32:  e = launch_prefill_t<float>(p, use_mma, use_tc, s); break;
+        case GQA_B200_F16:  e = launch_prefill_t<__half>(p, use_mma, use_tc, s); break;
+        default:            e = launch_prefill_t<__nv_bfloat16>(p, use_mma, use_tc, s); break;
     }
     return (int)e;
+}
+
+int gqa_b200_prefill_tc_status(int reset) {
+    int* status = nullptr;
+    cudaError_t e = prefill_tc_status_address(&status);
+    if (e != cudaSuccess) return -(int)e;
+    int host = 0;
+    e = cudaMemcpy(&host, status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return -(int)e;
+    if (reset) {
+        const int zero = 0;
+        e = cudaMemcpy(status, &zero, sizeof(int), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) return -(int)e;
+    }
+    return host;
 }
 
 int gqa_b200_kv_append(const void* key, const void* value, void* k_cache, void* v_cache,

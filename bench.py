@@ -48,6 +48,11 @@ def parse_args():
     p.add_argument("--steps", type=int, default=200)
     p.add_argument("--warmup", type=int, default=20)
     p.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    p.add_argument("--op", choices=["decode", "prefill"], default="decode",
+                   help="decode (the headline metric, default) or the dense prefill operator")
+    p.add_argument("--prefill-batch", type=int, default=4)
+    p.add_argument("--prefill-seq", type=int, default=4096)
+    p.add_argument("--prefill-kernel", default="auto", choices=["auto", "simt", "mma", "tcgen05"])
     p.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=list(synth.WORKLOADS))
     p.add_argument("--seed", type=int, default=42)
     p.add_argument("--kernel", default="auto", choices=["auto", "simt", "mma"])
@@ -460,8 +465,82 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------- prefill (secondary)
+def run_prefill(args):
+    """Dense GQA prefill throughput: one JSON line with TFLOP/s of one ``gqa_prefill`` call on a
+    full causal batch (4 * B * Hq * D * T^2 / 2 flops), the roofline against the measured dense
+    bf16 tensor peak, and the CPU restatement of the reference timed on a bounded sample."""
+    import attention_b200 as attn
+
+    if not torch.cuda.is_available() or not attn.is_cuda_extension_loaded():
+        raise RuntimeError("needs a CUDA device and the built C-ABI library (no CPU fallback)")
+    dev = torch.device("cuda", 0)
+    b, t, hq, hkv, d = args.prefill_batch, args.prefill_seq, 32, 8, 128
+    gen = torch.Generator(device=dev).manual_seed(args.seed)
+    q = torch.empty(b, t, hq, d, device=dev, dtype=torch.bfloat16).normal_(generator=gen)
+    k = torch.empty(b, t, hkv, d, device=dev, dtype=torch.bfloat16).normal_(generator=gen)
+    v = torch.empty(b, t, hkv, d, device=dev, dtype=torch.bfloat16).normal_(generator=gen)
+    lens = torch.full((b,), t, dtype=torch.int32, device=dev)
+
+    def step():
+        return attn.gqa_prefill(q, k, v, lens, lens, causal=True, kernel=args.prefill_kernel)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    t0 = time.perf_counter()
+    while time.perf_counter() - t0 < args.spinup_seconds:
+        step()
+        torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(0))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with sampler:
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        sampler.sample()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = 4.0 * b * hq * d * t * t * 0.5
+    tflops = flops / ms / 1e9
+    try:
+        peak = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"])
+        src = "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    except (OSError, KeyError, ValueError):
+        peak, src = 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+    line = {
+        "metric": "gqa_prefill_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "vs_baseline": None,
+        "config": {"workload": f"dense causal prefill B{b} T{t} {hq}/{hkv} heads D{d}",
+                   "kernel": args.prefill_kernel, "flops_per_step": flops},
+        "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s",
+                     "frac": tflops / peak, "peak_source": src, "traffic": None},
+        "gpu_launches": args.steps, "clocks": sampler.summary(),
+    }
+    if not args.no_cpu_baseline:
+        from oracle import gqa_oracle
+        n = min(t, 512)     # bounded sample: the first 512 query rows / keys of one sequence
+        cq, ck, cv = q[:1, :n].cpu(), k[:1, :n].cpu(), v[:1, :n].cpu()
+        cl = torch.tensor([n], dtype=torch.int32)
+        threads = len(os.sched_getaffinity(0))
+        torch.set_num_threads(threads)
+        gqa_oracle.reference_gqa_prefill(cq, ck, cv, cl, cl)
+        t0 = time.perf_counter()
+        gqa_oracle.reference_gqa_prefill(cq, ck, cv, cl, cl)
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": 4.0 * hq * d * n * n * 0.5 / dt / 1e12, "unit": "TFLOP/s",
+                                "cores": threads, "kind": "port", "seconds": dt,
+                                "sample": f"first {n} rows/keys of one sequence, torch fp32 "
+                                          "restatement of the reference oracle"}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
+    if args.op == "prefill":
+        run_prefill(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -41,6 +41,9 @@ extern "C" {
 #define GQA_B200_KERNEL_MMA 2  /* mma.sync m16n8k16; fp16/bf16, D in {64,128,256},
                                   16-byte aligned tensors                        */
 
+#define GQA_B200_KERNEL_TCGEN05 4 /* prefill only: tcgen05.mma with TMEM accumulators;
+                                  same shapes as GQA_B200_KERNEL_MMA               */
+
 /* status codes (negative = invalid argument) */
 #define GQA_B200_OK 0
 #define GQA_B200_ERR_NULL_POINTER (-1)
@@ -200,12 +203,17 @@ GQA_B200_API int gqa_b200_decode_split(const void* q, const void* k_cache, const
  * 0 .. kv_len - q_len + i when `causal` (right-aligned causal mask,
  * csrc/cuda/common/tile_utils.cuh:6-9), else to all kv_len keys; rows at or past
  * q_len, and rows that see no key, are written as zeros.  One kernel launch, no
- * scratch.  `kernel`: GQA_B200_KERNEL_AUTO / _SIMT / _MMA (fp16/bf16, head_dim
- * 64 or 128, 16-byte aligned tensors). */
+ * scratch.  `kernel`: GQA_B200_KERNEL_AUTO / _SIMT / _MMA / _TCGEN05 (the last two:
+ * fp16/bf16, head_dim 64 or 128, 16-byte aligned tensors). */
 GQA_B200_API int gqa_b200_prefill(const void* q, const void* k, const void* v,
                                   const int32_t* q_lens, const int32_t* kv_lens, void* out,
                                   int dtype, int batch, int tq, int tk, int q_heads, int kv_heads,
                                   int head_dim, float scale, int causal, int kernel, void* stream);
+
+/* Debug aid for the tcgen05 prefill kernel: synchronises, returns its device status word
+ * (0 ok, 2 = a bounded mbarrier wait ran out, 3 = misaligned shared memory; negative = a
+ * cudaError_t) and clears it when `reset` is non-zero.  Not for a hot path. */
+GQA_B200_API int gqa_b200_prefill_tc_status(int reset);
 
 /* Write one new token per sequence into its page.  Replaces kv_append_cuda
  * (csrc/cuda/cache/kv_append.cu:29-56): key/value are [batch, kv_heads,

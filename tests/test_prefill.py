@@ -53,11 +53,18 @@ def _case(b, tq, tk, hq, hkv, d, dtype, q_lens, kv_lens, seed=0):
             torch.tensor(kv_lens, dtype=torch.int32, device=DEV))
 
 
+def _tc_ok(dtype, d):
+    """Shapes the tensor-core kernels (mma.sync and tcgen05) take."""
+    return dtype in (torch.float16, torch.bfloat16) and d in (64, 128)
+
+
 @pytest.mark.gpu
-@pytest.mark.parametrize("kernel", ["auto", "simt"])
+@pytest.mark.parametrize("kernel", ["auto", "simt", "mma", "tcgen05"])
 @pytest.mark.parametrize("name", prefill_cases())
 def test_prefill_golden(name, kernel):
     q, k, v, ql, kl, causal, scale, want = load_prefill(name)
+    if kernel in ("mma", "tcgen05") and not _tc_ok(q.dtype, q.shape[-1]):
+        pytest.skip("shape not covered by the tensor-core kernels")
     got = attn.gqa_prefill(q.to(DEV), k.to(DEV), v.to(DEV), ql.to(DEV), kl.to(DEV), causal=causal,
                            scale=scale, kernel=kernel)
     _close(got, want, q.dtype, f"{name} {kernel}")
@@ -73,7 +80,8 @@ def test_prefill_ragged_batches(dtype, causal):
     kv_lens = [5, 1, 63, 64, 65, 300, 150, 300, 0, 200]
     args = _case(10, 200, 300, 8, 2, 128, dtype, q_lens, kv_lens, seed=3)
     want = gqa_oracle.reference_gqa_prefill(*args, causal=causal)
-    for kernel in ("auto", "simt"):
+    kernels = ("auto", "simt", "mma", "tcgen05") if _tc_ok(dtype, 128) else ("auto", "simt")
+    for kernel in kernels:
         got = attn.gqa_prefill(*args, causal=causal, kernel=kernel)
         _close(got, want, dtype, f"{dtype} causal={causal} {kernel}")
         assert torch.count_nonzero(got[0]) == 0 and torch.count_nonzero(got[8]) == 0
@@ -87,16 +95,35 @@ def test_prefill_head_layouts_and_sizes(hq, hkv, d):
     want = gqa_oracle.reference_gqa_prefill(*args)
     _close(attn.gqa_prefill(*args), want, torch.bfloat16, f"{hq}/{hkv} D={d}")
     _close(attn.gqa_prefill(*args, backend="tensorcore"), want, torch.bfloat16)
+    if _tc_ok(torch.bfloat16, d):
+        for kernel in ("mma", "tcgen05"):
+            _close(attn.gqa_prefill(*args, kernel=kernel), want, torch.bfloat16, f"{kernel} D={d}")
+    else:
+        with pytest.raises(RuntimeError, match="kernel"):
+            attn.gqa_prefill(*args, kernel="tcgen05")
 
 
 @pytest.mark.gpu
 def test_prefill_long_sequence_and_scale():
     args = _case(1, 2048, 2048, 8, 2, 128, torch.bfloat16, [2048], [2048], seed=9)
     want = gqa_oracle.reference_gqa_prefill(*args, scale=0.05)
-    _close(attn.gqa_prefill(*args, scale=0.05), want, torch.bfloat16, "2k causal")
+    for kernel in ("mma", "tcgen05"):
+        _close(attn.gqa_prefill(*args, scale=0.05, kernel=kernel), want, torch.bfloat16,
+               f"2k causal {kernel}")
     args = _case(2, 33, 4096, 8, 2, 128, torch.float16, [33, 20], [4096, 3000], seed=10)
     want = gqa_oracle.reference_gqa_prefill(*args)
-    _close(attn.gqa_prefill(*args), want, torch.float16, "chunked over 4k prefix")
+    for kernel in ("mma", "tcgen05"):
+        _close(attn.gqa_prefill(*args, kernel=kernel), want, torch.float16,
+               f"chunked over 4k prefix {kernel}")
+
+
+@pytest.mark.gpu
+def test_prefill_tcgen05_status_word_stays_clear():
+    """The tcgen05 kernel's bounded waits never ran out in the calls above (or here)."""
+    from attention_b200 import _cabi
+    args = _case(2, 260, 260, 8, 2, 128, torch.bfloat16, [260, 100], [260, 100], seed=12)
+    attn.gqa_prefill(*args, kernel="tcgen05")
+    assert _cabi.load().gqa_b200_prefill_tc_status(0) == 0
 
 
 @pytest.mark.gpu
