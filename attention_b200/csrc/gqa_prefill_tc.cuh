@@ -2,16 +2,20 @@
 // head_dim 64 / 128.
 //
 // One CTA = one query head x 128 query rows.  Both contractions are single-thread-issued
-// tcgen05.mma (cta_group::1, kind::f16) with operands in shared memory as K-major
-// 128-byte-swizzled tiles and fp32 accumulators in TMEM:
-//   S[128 x 64]  = Q[128 x D] . K_tile[64 x D]^T          (TMEM columns 0..63)
-//   O[128 x D]  += P[128 x 64] . Vt_tile[D x 64]^T        (TMEM columns 64..64+D)
-// K/V tiles arrive with 16-byte cp.async; V ([key][d] in memory) is transposed into the
-// K-major tile Vt with ldmatrix.trans + stmatrix.  The softmax is thread-per-row: thread r
-// reads row r of S from TMEM (no shuffles), keeps the fp32 running (max, sum), writes its
-// row of P as a swizzled 128-byte row, and rescales its row of O in TMEM only when the
-// row maximum moved by more than 2^8 (lazy rescaling).  Two CTAs fit per SM (112 KB of
-// shared memory, 256 TMEM columns each), so one CTA's softmax overlaps the other's MMAs.
+// tcgen05.mma (cta_group::1, kind::f16) with operands in shared memory as 128-byte-swizzled
+// tiles and fp32 accumulators in TMEM:
+//   S[128 x 64]  = Q[128 x D] . K_tile[64 x D]^T     Q, K: K-major tiles    (TMEM: two S buffers)
+//   O[128 x D]  += P[128 x 64] . V_tile[64 x D]      V: used as it lies in memory ([key][d]),
+//                                                    as an MN-major B operand    (TMEM: D columns)
+// K and V tiles arrive with 16-byte cp.async into two-stage rings.  The softmax is
+// thread-per-row: thread r reads row r of S from TMEM (no shuffles), keeps the fp32 running
+// (max, sum), writes its row of P as a swizzled 128-byte row, and rescales its row of O in
+// TMEM only when the row maximum moved by more than 2^8 (lazy rescaling).
+//
+// Software pipeline (iteration j = softmax of tile j): S(j+1) = Q.K(j+1)^T is issued before
+// the softmax of tile j starts, so the tensor cores work on the next scores (and on the
+// previous P.V) while the threads exponentiate; P.V(j) is issued as soon as P(j) is in
+// shared memory.  Two CTAs fit per SM (112 KB of shared memory, 256 TMEM columns each).
 //
 // Every mbarrier wait is bounded; a wait that runs out marks the CTA dead (later waits
 // give up at once), raises the status word and the kernel still frees its TMEM.
@@ -32,16 +36,13 @@ constexpr int kTcThreads = 128;
 constexpr int kTcTmemCols = 256;
 
 template <int D> struct PrefillTcGeom {
-    static constexpr int kKB = D / 64;                        // 128-byte K blocks of Q / K rows
+    static constexpr int kKB = D / 64;                        // 128-byte blocks of a Q/K/V row
     static constexpr int kQBytes = kKB * kTcBM * 128;
-    static constexpr int kKTileBytes = kKB * kTcBN * 128;
-    static constexpr int kVRawBytes = kTcBN * D * 2;
-    static constexpr int kVtBytes = D * 128;                  // [D rows][64 keys x 2 B]
+    static constexpr int kTileBytes = kKB * kTcBN * 128;      // one K or V tile
     static constexpr int kPBytes = kTcBM * 128;
     static constexpr int kOffK = kQBytes;
-    static constexpr int kOffVRaw = kOffK + 2 * kKTileBytes;
-    static constexpr int kOffVt = kOffVRaw + kVRawBytes;
-    static constexpr int kOffP = kOffVt + kVtBytes;
+    static constexpr int kOffV = kOffK + 2 * kTileBytes;
+    static constexpr int kOffP = kOffV + 2 * kTileBytes;
     static constexpr int kSmemBytes = kOffP + kPBytes;
 };
 
@@ -52,15 +53,14 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
     using Ops = MmaOps<T>;
     constexpr int BM = kTcBM, BN = kTcBN, NT = kTcThreads;
     constexpr int KB = G::kKB;
-    constexpr int AB_TYPE = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-    constexpr int VROWB = D * 2, VCPR = VROWB / 16;
+    constexpr int AB_TYPE = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
 
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ __align__(8) uint64_t s_bar[2];     // [0] S ready, [1] P.V done
+    __shared__ __align__(8) uint64_t s_bar[3];     // [0], [1]: S buffer ready; [2]: P.V done
     __shared__ uint32_t s_tmem;
     __shared__ int s_dead;
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5;
     const int qt = gridDim.x - 1 - blockIdx.x;     // heavy (late) query tiles first
     const int h = blockIdx.y, b = blockIdx.z;
     const int kvh = h / p.group;
@@ -90,60 +90,50 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
         if (tid == 0 && status) atomicExch(status, 3);
         return;
     }
-    const uint32_t sq = s_base, sk = s_base + G::kOffK, svraw = s_base + G::kOffVRaw;
-    const uint32_t svt = s_base + G::kOffVt, sp = s_base + G::kOffP;
-    const uint32_t bar_s = tc::smem_u32(&s_bar[0]), bar_pv = tc::smem_u32(&s_bar[1]);
+    const uint32_t sq = s_base, sk = s_base + G::kOffK, sv = s_base + G::kOffV, sp = s_base + G::kOffP;
+    const uint32_t bar_s0 = tc::smem_u32(&s_bar[0]), bar_pv = tc::smem_u32(&s_bar[2]);
 
     if (warp == 0) { tc::tmem_alloc(tc::smem_u32(&s_tmem), kTcTmemCols); tc::tmem_relinquish(); }
     if (tid == 0) {
-        tc::mbar_init(bar_s, 1);
+        tc::mbar_init(bar_s0, 1);
+        tc::mbar_init(bar_s0 + 8, 1);
         tc::mbar_init(bar_pv, 1);
         tc::fence_mbar_init();
         s_dead = 0;
     }
 
-    // ---- asynchronous copies into swizzled tiles ----
+    // ---- asynchronous copies into swizzled tiles: [64-element block][row][128 B] ----
     auto load_q = [&]() {
         for (int i = tid; i < BM * D / 8; i += NT) {
             const int row = i / (D / 8), c = i % (D / 8);
-            const int kb = c >> 3, cc = c & 7;
             const int qrow = m0 + row;
             const bool valid = qrow < q_len;
             const T* src = qp + (((size_t)b * p.tq + (valid ? qrow : 0)) * p.q_heads + h) * D + c * 8;
-            cp_async16<0>(sq + kb * (BM * 128) + row * 128 + ((cc ^ (row & 7)) << 4), src, valid ? 16 : 0, 0);
-        }
-    };
-    auto load_k = [&](int j) {
-        const uint32_t dst0 = sk + (j & 1) * G::kKTileBytes;
-        for (int i = tid; i < BN * D / 8; i += NT) {
-            const int row = i / (D / 8), c = i % (D / 8);
-            const int kb = c >> 3, cc = c & 7;
-            const int t = j * BN + row;
-            const bool valid = t < kv_len;
-            const size_t off = ((((size_t)b * p.tk + (valid ? t : 0)) * p.kv_heads + kvh) * D) * 2 + c * 16;
-            cp_async16<0>(dst0 + kb * (BN * 128) + row * 128 + ((cc ^ (row & 7)) << 4), kp + off,
+            cp_async16<0>(sq + (c >> 3) * (BM * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4), src,
                           valid ? 16 : 0, 0);
         }
     };
-    auto load_v = [&](int j) {
-        for (int i = tid; i < BN * VCPR; i += NT) {
-            const int row = i / VCPR, cc = i % VCPR;
+    auto load_tile = [&](const char* base, uint32_t dst0, int j) {   // K or V tile j (keys are rows)
+        for (int i = tid; i < BN * D / 8; i += NT) {
+            const int row = i / (D / 8), c = i % (D / 8);
             const int t = j * BN + row;
             const bool valid = t < kv_len;
-            const size_t off = ((((size_t)b * p.tk + (valid ? t : 0)) * p.kv_heads + kvh) * D) * 2 + cc * 16;
-            cp_async16<0>(svraw + row * VROWB + ((cc ^ (row & 7)) << 4), vp + off, valid ? 16 : 0, 0);
+            const size_t off = ((((size_t)b * p.tk + (valid ? t : 0)) * p.kv_heads + kvh) * D) * 2 + c * 16;
+            cp_async16<0>(dst0 + (c >> 3) * (BN * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4),
+                          base + off, valid ? 16 : 0, 0);
         }
     };
 
     load_q();
-    load_k(0);
-    load_v(0);
+    load_tile(kp, sk, 0);
+    load_tile(vp, sv, 0);
+    if (n_tiles > 1) load_tile(kp, sk + G::kTileBytes, 1);
     cp_async_commit();
 
     const int my_end = my_row < q_len ? prefill_row_end(my_row, q_len, kv_len, p.causal) : 0;
     float m_run = -INFINITY, l_run = 0.f;
     const uint32_t idesc_s = tc::idesc_f16(BM, BN, AB_TYPE);
-    const uint32_t idesc_o = tc::idesc_f16(BM, D, AB_TYPE);
+    const uint32_t idesc_o = tc::idesc_f16(BM, D, AB_TYPE) | tc::kIdescBMnMajor;
     const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;      // this warp's TMEM lanes
     bool alive = true;
 
@@ -155,64 +145,49 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
             if (status) atomicExch(status, 2);
         }
     };
+    // S(j) = Q K(j)^T into S buffer j & 1 (one thread)
+    auto issue_qk = [&](int j, uint32_t tmem) {
+        const uint32_t kt = sk + (j & 1) * G::kTileBytes;
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint64_t da = tc::smem_desc_sw128_kmajor(sq + kb * (BM * 128) + k * 32);
+                const uint64_t db = tc::smem_desc_sw128_kmajor(kt + kb * (BN * 128) + k * 32);
+                tc::mma_f16_ss(tmem + (j & 1) * BN, da, db, idesc_s, (kb | k) ? 1u : 0u);
+            }
+        }
+        tc::mma_commit(bar_s0 + (j & 1) * 8);
+    };
 
-    __syncthreads();                               // s_tmem, barriers, s_dead visible
+    cp_async_wait<0>();
+    tc::fence_async_smem();
+    tc::tc_fence_before();
+    __syncthreads();                               // Q, K(0..1), V(0) in place; s_tmem, barriers visible
     tc::tc_fence_after();
     const uint32_t tmem = s_tmem;
-    const uint32_t tmem_s = tmem, tmem_o = tmem + BN;
+    const uint32_t tmem_o = tmem + 2 * BN;
+    if (tid == 0) issue_qk(0, tmem);
 
     for (int j = 0; j < n_tiles; ++j) {
-        // ---- tile j has landed; the P.V of tile j-1 no longer reads Vt / P ----
-        cp_async_wait<0>();
-        tc::fence_async_smem();
-        if (j > 0) wait_bar(bar_pv, (j - 1) & 1);
-        __syncthreads();
-
-        // ---- V [key][d]  ->  Vt [d][key], K-major swizzled (8 x4 ops per warp for D = 128) ----
-        for (int x = warp; x < (D / 8) * (BN / 8) / 4; x += NT / 32) {
-            // four 8x8 blocks: key blocks kb0..kb0+3 of one d block
-            const int db = x / (BN / 32), kb0 = (x % (BN / 32)) * 4;
-            const int blk = lane >> 3, i = lane & 7;
-            const int key_row = (kb0 + blk) * 8 + i;
-            uint32_t r0, r1, r2, r3;
-            ldmatrix_x4_trans(svraw + key_row * VROWB + ((db ^ (key_row & 7)) << 4), r0, r1, r2, r3);
-            const int d_row = db * 8 + i;
-            tc::stmatrix_x4(svt + d_row * 128 + (((kb0 + blk) ^ (d_row & 7)) << 4), r0, r1, r2, r3);
-        }
-        tc::fence_async_smem();
-        tc::tc_fence_before();
-        __syncthreads();                           // Vt complete; raw V stage free again
-
-        if (j + 1 < n_tiles) { load_k(j + 1); load_v(j + 1); }
+        // ---- S(j) is ready, so K stage j&1 is free: fetch K(j+2) into it ----
+        wait_bar(bar_s0 + (j & 1) * 8, (j >> 1) & 1);
+        tc::tc_fence_after();
+        if (j + 2 < n_tiles) load_tile(kp, sk + (j & 1) * G::kTileBytes, j + 2);
         cp_async_commit();
 
-        // ---- S = Q K^T ----
-        if (tid == 0) {
-            tc::tc_fence_after();
-            const uint32_t kt = sk + (j & 1) * G::kKTileBytes;
-#pragma unroll
-            for (int kb = 0; kb < KB; ++kb) {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint64_t da = tc::smem_desc_sw128_kmajor(sq + kb * (BM * 128) + k * 32);
-                    const uint64_t db = tc::smem_desc_sw128_kmajor(kt + kb * (BN * 128) + k * 32);
-                    tc::mma_f16_ss(tmem_s, da, db, idesc_s, (kb | k) ? 1u : 0u);
-                }
-            }
-            tc::mma_commit(bar_s);
-        }
-        wait_bar(bar_s, j & 1);
-        tc::tc_fence_after();
+        // ---- start S(j+1) on the tensor cores before exponentiating tile j ----
+        if (j + 1 < n_tiles && tid == 0) issue_qk(j + 1, tmem);
 
-        // ---- softmax of this thread's row ----
+        // ---- scores of this thread's row: mask, running max, probabilities (registers) ----
         float s[BN];
         {
             uint32_t r[32];
-            tc::tmem_ld32(tmem_s + lane_sel, r);
+            tc::tmem_ld32(tmem + (j & 1) * BN + lane_sel, r);
             tc::tmem_ld_wait();
 #pragma unroll
             for (int c = 0; c < 32; ++c) s[c] = __uint_as_float(r[c]);
-            tc::tmem_ld32(tmem_s + lane_sel + 32, r);
+            tc::tmem_ld32(tmem + (j & 1) * BN + lane_sel + 32, r);
             tc::tmem_ld_wait();
 #pragma unroll
             for (int c = 0; c < 32; ++c) s[32 + c] = __uint_as_float(r[c]);
@@ -228,56 +203,64 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
         for (int c = 1; c < BN; ++c) mx = fmaxf(mx, s[c]);
         mx *= p.scale_log2;
         const bool need = mx > m_run + kRescaleSlack;
-        if (__any_sync(0xffffffffu, need)) {        // warp-uniform: TMEM ld/st are warp-collective
-            float alpha = 1.f;
-            if (need) {
-                const float mn = fmaxf(m_run, mx);
-                alpha = m_run == -INFINITY ? 0.f : fast_exp2(m_run - mn);
-                m_run = mn;
-                l_run *= alpha;
-            }
-            if (j > 0) {                           // O holds nothing before the first P.V
-#pragma unroll
-                for (int c0 = 0; c0 < D; c0 += 32) {
-                    uint32_t r[32];
-                    tc::tmem_ld32(tmem_o + lane_sel + c0, r);
-                    tc::tmem_ld_wait();
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
-                    tc::tmem_st32(tmem_o + lane_sel + c0, r);
-                }
-                tc::tmem_st_wait();
-            }
+        float alpha = 1.f;
+        if (need) {
+            const float mn = fmaxf(m_run, mx);
+            alpha = m_run == -INFINITY ? 0.f : fast_exp2(m_run - mn);
+            m_run = mn;
+            l_run *= alpha;
         }
         const float ref = m_run == -INFINITY ? 0.f : m_run;
+        uint32_t pw[BN / 2];
         {
             float psum = 0.f;
 #pragma unroll
-            for (int c8 = 0; c8 < BN / 8; ++c8) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = fast_exp2(fmaf(s[c8 * 8 + 2 * e], p.scale_log2, -ref));
-                    const float p1 = fast_exp2(fmaf(s[c8 * 8 + 2 * e + 1], p.scale_log2, -ref));
-                    psum += p0 + p1;
-                    w[e] = Ops::pack(p0, p1);
-                }
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(sp + tid * 128 + ((c8 ^ (tid & 7)) << 4)),
-                             "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+            for (int c2 = 0; c2 < BN / 2; ++c2) {
+                const float p0 = fast_exp2(fmaf(s[2 * c2], p.scale_log2, -ref));
+                const float p1 = fast_exp2(fmaf(s[2 * c2 + 1], p.scale_log2, -ref));
+                psum += p0 + p1;
+                pw[c2] = Ops::pack(p0, p1);
             }
             l_run += psum;
         }
+
+        // ---- P.V(j-1) is done: V stage (j+1)&1, the P tile and O may be touched ----
+        if (j > 0) wait_bar(bar_pv, (j - 1) & 1);
+        tc::tc_fence_after();
+        if (j + 1 < n_tiles) load_tile(vp, sv + ((j + 1) & 1) * G::kTileBytes, j + 1);
+        cp_async_commit();
+        if (j > 0 && __any_sync(0xffffffffu, need)) {   // warp-uniform: TMEM ld/st are collective
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t r[32];
+                tc::tmem_ld32(tmem_o + lane_sel + c0, r);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+                tc::tmem_st32(tmem_o + lane_sel + c0, r);
+            }
+            tc::tmem_st_wait();
+        }
+#pragma unroll
+        for (int c8 = 0; c8 < BN / 8; ++c8) {
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(sp + tid * 128 + ((c8 ^ (tid & 7)) << 4)),
+                         "r"(pw[c8 * 4 + 0]), "r"(pw[c8 * 4 + 1]), "r"(pw[c8 * 4 + 2]), "r"(pw[c8 * 4 + 3])
+                         : "memory");
+        }
+        // V(j) (issued one iteration ago) and K(j+1) must have landed for everyone
+        cp_async_wait<1>();
         tc::fence_async_smem();
         tc::tc_fence_before();
-        __syncthreads();                           // P complete; all reads of S and O rescales done
+        __syncthreads();                           // P complete, S(j) consumed, O rescaled, V(j) in place
 
-        // ---- O += P V ----
+        // ---- O += P V(j) ----
         if (tid == 0) {
             tc::tc_fence_after();
+            const uint32_t vt = sv + (j & 1) * G::kTileBytes;
 #pragma unroll
             for (int k = 0; k < BN / 16; ++k) {
                 const uint64_t da = tc::smem_desc_sw128_kmajor(sp + k * 32);
-                const uint64_t db = tc::smem_desc_sw128_kmajor(svt + k * 32);
+                const uint64_t db = tc::smem_desc_sw128_mnmajor(vt + k * 2048, BN * 128);
                 tc::mma_f16_ss(tmem_o, da, db, idesc_o, (j | k) ? 1u : 0u);
             }
             tc::mma_commit(bar_pv);

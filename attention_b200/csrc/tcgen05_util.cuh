@@ -61,6 +61,23 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_kmajor(uint32_t saddr) {
     d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
     return d;
 }
+// shared-memory matrix descriptor, MN-major operand tile with 128-byte swizzle: the tile
+// is [MN blocks of 64 elements][K rows][128 bytes] (an operand stored [k][mn] in memory, 64
+// mn-elements per 128-byte row segment), 16-byte chunk c of K row k at chunk (c ^ (k & 7)).
+// Leading byte offset = distance between MN blocks, stride byte offset = 8 K rows = 1024;
+// one K = 16 step of the MMA covers 16 rows = 2048 bytes.  (Verified against a reference
+// product on B200 together with bit 16 of the instruction descriptor.)
+__device__ __forceinline__ uint64_t smem_desc_sw128_mnmajor(uint32_t saddr, uint32_t mn_block_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((mn_block_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+constexpr uint32_t kIdescBMnMajor = 1u << 16;
+
 // instruction descriptor for kind::f16: D fp32, A/B both K-major, type 0 = f16, 1 = bf16
 __device__ __forceinline__ uint32_t idesc_f16(int m, int n, int ab_type) {
     uint32_t d = 0;
