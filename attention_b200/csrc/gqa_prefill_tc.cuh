@@ -113,14 +113,26 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
                           valid ? 16 : 0, 0);
         }
     };
-    auto load_tile = [&](const char* base, uint32_t dst0, int j) {   // K or V tile j (keys are rows)
-        for (int i = tid; i < BN * D / 8; i += NT) {
-            const int row = i / (D / 8), c = i % (D / 8);
-            const int t = j * BN + row;
-            const bool valid = t < kv_len;
-            const size_t off = ((((size_t)b * p.tk + (valid ? t : 0)) * p.kv_heads + kvh) * D) * 2 + c * 16;
-            cp_async16<0>(dst0 + (c >> 3) * (BN * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4),
-                          base + off, valid ? 16 : 0, 0);
+    // K or V tile j (keys are rows).  Each thread always copies the same 16-byte chunk of
+    // rows row0, row0 + RPI, ...: since RPI is a multiple of 8 the swizzle term is constant,
+    // so source and destination advance by fixed steps (no per-copy address arithmetic).
+    constexpr int CPRW = D / 8;                    // 16-byte chunks per row
+    constexpr int RPI = NT / CPRW;                 // rows covered by one pass of the CTA
+    static_assert(RPI % 8 == 0 && BN % RPI == 0, "copy pattern");
+    const int ld_c = tid % CPRW, ld_row0 = tid / CPRW;
+    const size_t row_stride = (size_t)p.kv_heads * D * 2;
+    const size_t thr_src = (size_t)ld_row0 * row_stride + (size_t)kvh * D * 2 + ld_c * 16;
+    const uint32_t thr_dst = (ld_c >> 3) * (BN * 128) + ld_row0 * 128 + (((ld_c & 7) ^ (ld_row0 & 7)) << 4);
+    auto load_tile = [&](const char* base, uint32_t dst0, int j) {
+        const char* src = base + ((size_t)b * p.tk + (size_t)j * BN) * row_stride + thr_src;
+        uint32_t dst = dst0 + thr_dst;
+        const int t0 = j * BN + ld_row0;
+#pragma unroll
+        for (int it = 0; it < BN / RPI; ++it) {
+            const bool valid = t0 + it * RPI < kv_len;
+            cp_async16<0>(dst, valid ? src : base, valid ? 16 : 0, 0);
+            src += (size_t)RPI * row_stride;
+            dst += RPI * 128;
         }
     };
 
