@@ -7,10 +7,12 @@
 //   S[128 x 64]  = Q[128 x D] . K_tile[64 x D]^T     Q, K: K-major tiles    (TMEM: two S buffers)
 //   O[128 x D]  += P[128 x 64] . V_tile[64 x D]      V: used as it lies in memory ([key][d]),
 //                                                    as an MN-major B operand    (TMEM: D columns)
-// K and V tiles arrive with 16-byte cp.async into two-stage rings.  The softmax is
-// thread-per-row: thread r reads row r of S from TMEM (no shuffles), keeps the fp32 running
-// (max, sum), writes its row of P as a swizzled 128-byte row, and rescales its row of O in
-// TMEM only when the row maximum moved by more than 2^8 (lazy rescaling).
+// K and V tiles arrive with 16-byte cp.async into two-stage rings.  The softmax uses two
+// threads per row (warps w and w + 4 own the same 32 TMEM lanes): both read row r of S from
+// TMEM and take its maximum (so they agree on the running max without talking to each
+// other), each exponentiates and sums its own half, writes its half of P as part of a
+// swizzled 128-byte row, and rescales its half of row r of O in TMEM only when the row
+// maximum moved by more than 2^8 (lazy rescaling).  The two half sums meet once, at the end.
 //
 // Software pipeline (iteration j = softmax of tile j): S(j+1) = Q.K(j+1)^T is issued before
 // the softmax of tile j starts, so the tensor cores work on the next scores (and on the
@@ -32,7 +34,7 @@ namespace gqa_b200 {
 
 constexpr int kTcBM = 128;
 constexpr int kTcBN = 64;
-constexpr int kTcThreads = 128;
+constexpr int kTcThreads = 256;
 constexpr int kTcTmemCols = 256;
 
 template <int D> struct PrefillTcGeom {
@@ -60,7 +62,9 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
     __shared__ uint32_t s_tmem;
     __shared__ int s_dead;
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quad = warp & 3, hf = warp >> 2;     // TMEM lane quadrant, column half
+    const int row_l = quad * 32 + lane;            // this thread's row of the 128-row tile
     const int qt = gridDim.x - 1 - blockIdx.x;     // heavy (late) query tiles first
     const int h = blockIdx.y, b = blockIdx.z;
     const int kvh = h / p.group;
@@ -71,16 +75,17 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
     const char* kp = reinterpret_cast<const char*>(p.k);
     const char* vp = reinterpret_cast<const char*>(p.v);
     T* op = reinterpret_cast<T*>(p.out);
-    const int my_row = m0 + tid;                   // thread-per-row
+    const int my_row = m0 + row_l;
 
     int tile_end = 0;
     if (m0 < q_len) tile_end = prefill_row_end(min(m0 + BM, q_len) - 1, q_len, kv_len, p.causal);
     const int n_tiles = (tile_end + BN - 1) / BN;
     if (n_tiles == 0) {                            // nothing visible: zero rows, no TMEM needed
         if (my_row < p.tq) {
-            uint4* dst = reinterpret_cast<uint4*>(op + (((size_t)b * p.tq + my_row) * p.q_heads + h) * D);
+            uint4* dst = reinterpret_cast<uint4*>(op + (((size_t)b * p.tq + my_row) * p.q_heads + h) * D) +
+                         hf * (D / 16);
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+            for (int c = 0; c < D / 16; ++c) dst[c] = make_uint4(0u, 0u, 0u, 0u);
         }
         return;
     }
@@ -146,7 +151,7 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
     float m_run = -INFINITY, l_run = 0.f;
     const uint32_t idesc_s = tc::idesc_f16(BM, BN, AB_TYPE);
     const uint32_t idesc_o = tc::idesc_f16(BM, D, AB_TYPE) | tc::kIdescBMnMajor;
-    const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;      // this warp's TMEM lanes
+    const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;      // this warp's TMEM lanes
     bool alive = true;
 
     auto wait_bar = [&](uint32_t bar, uint32_t parity) {
@@ -191,29 +196,43 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
         // ---- start S(j+1) on the tensor cores before exponentiating tile j ----
         if (j + 1 < n_tiles && tid == 0) issue_qk(j + 1, tmem);
 
-        // ---- scores of this thread's row: mask, running max, probabilities (registers) ----
-        float s[BN];
+        // ---- scores of this thread's row: own half kept, the other half only for the maximum ----
+        constexpr int HC = BN / 2;                 // columns per thread
+        float s[HC];
+        float mx;
         {
             uint32_t r[32];
-            tc::tmem_ld32(tmem + (j & 1) * BN + lane_sel, r);
+            tc::tmem_ld32(tmem + (j & 1) * BN + lane_sel + (hf ^ 1) * HC, r);   // the other half
+            tc::tmem_ld_wait();
+            const int t_other = j * BN + (hf ^ 1) * HC;
+            float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
+            if (t_other + HC > my_end) {
+#pragma unroll
+                for (int c = 0; c < HC; ++c)
+                    if (t_other + c >= my_end) r[c] = 0xff800000u;   // -inf
+            }
+#pragma unroll
+            for (int c = 0; c < HC; c += 4) {
+                a0 = fmaxf(a0, __uint_as_float(r[c])); a1 = fmaxf(a1, __uint_as_float(r[c + 1]));
+                a2 = fmaxf(a2, __uint_as_float(r[c + 2])); a3 = fmaxf(a3, __uint_as_float(r[c + 3]));
+            }
+            tc::tmem_ld32(tmem + (j & 1) * BN + lane_sel + hf * HC, r);         // this thread's half
             tc::tmem_ld_wait();
 #pragma unroll
-            for (int c = 0; c < 32; ++c) s[c] = __uint_as_float(r[c]);
-            tc::tmem_ld32(tmem + (j & 1) * BN + lane_sel + 32, r);
-            tc::tmem_ld_wait();
+            for (int c = 0; c < HC; ++c) s[c] = __uint_as_float(r[c]);
+            const int t_base = j * BN + hf * HC;
+            if (t_base + HC > my_end) {
 #pragma unroll
-            for (int c = 0; c < 32; ++c) s[32 + c] = __uint_as_float(r[c]);
+                for (int c = 0; c < HC; ++c)
+                    if (t_base + c >= my_end) s[c] = -INFINITY;
+            }
+#pragma unroll
+            for (int c = 0; c < HC; c += 4) {
+                a0 = fmaxf(a0, s[c]); a1 = fmaxf(a1, s[c + 1]);
+                a2 = fmaxf(a2, s[c + 2]); a3 = fmaxf(a3, s[c + 3]);
+            }
+            mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * p.scale_log2;
         }
-        const int t_base = j * BN;
-        if (t_base + BN > my_end) {
-#pragma unroll
-            for (int c = 0; c < BN; ++c)
-                if (t_base + c >= my_end) s[c] = -INFINITY;
-        }
-        float mx = s[0];
-#pragma unroll
-        for (int c = 1; c < BN; ++c) mx = fmaxf(mx, s[c]);
-        mx *= p.scale_log2;
         const bool need = mx > m_run + kRescaleSlack;
         float alpha = 1.f;
         if (need) {
@@ -223,17 +242,20 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
             l_run *= alpha;
         }
         const float ref = m_run == -INFINITY ? 0.f : m_run;
-        uint32_t pw[BN / 2];
+        uint32_t pw[HC / 2];
         {
-            float psum = 0.f;
+            float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;   // independent partial sums
 #pragma unroll
-            for (int c2 = 0; c2 < BN / 2; ++c2) {
+            for (int c2 = 0; c2 < HC / 2; c2 += 2) {
                 const float p0 = fast_exp2(fmaf(s[2 * c2], p.scale_log2, -ref));
                 const float p1 = fast_exp2(fmaf(s[2 * c2 + 1], p.scale_log2, -ref));
-                psum += p0 + p1;
+                const float p2 = fast_exp2(fmaf(s[2 * c2 + 2], p.scale_log2, -ref));
+                const float p3 = fast_exp2(fmaf(s[2 * c2 + 3], p.scale_log2, -ref));
+                ps0 += p0; ps1 += p1; ps2 += p2; ps3 += p3;
                 pw[c2] = Ops::pack(p0, p1);
+                pw[c2 + 1] = Ops::pack(p2, p3);
             }
-            l_run += psum;
+            l_run += (ps0 + ps1) + (ps2 + ps3);     // this thread's half of the row sum
         }
 
         // ---- P.V(j-1) is done: V stage (j+1)&1, the P tile and O may be touched ----
@@ -243,7 +265,7 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
         cp_async_commit();
         if (j > 0 && __any_sync(0xffffffffu, need)) {   // warp-uniform: TMEM ld/st are collective
 #pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
+            for (int c0 = hf * (D / 2); c0 < (hf + 1) * (D / 2); c0 += 32) {
                 uint32_t r[32];
                 tc::tmem_ld32(tmem_o + lane_sel + c0, r);
                 tc::tmem_ld_wait();
@@ -254,8 +276,9 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
             tc::tmem_st_wait();
         }
 #pragma unroll
-        for (int c8 = 0; c8 < BN / 8; ++c8) {
-            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(sp + tid * 128 + ((c8 ^ (tid & 7)) << 4)),
+        for (int c8 = 0; c8 < HC / 8; ++c8) {
+            const int chunk = hf * (HC / 8) + c8;
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(sp + row_l * 128 + ((chunk ^ (row_l & 7)) << 4)),
                          "r"(pw[c8 * 4 + 0]), "r"(pw[c8 * 4 + 1]), "r"(pw[c8 * 4 + 2]), "r"(pw[c8 * 4 + 3])
                          : "memory");
         }
@@ -281,10 +304,15 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
     wait_bar(bar_pv, (n_tiles - 1) & 1);
     tc::tc_fence_after();
 
-    // ---- normalise and store this thread's row ----
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    // ---- row sum = sum of the two halves (exchanged through the idle P tile); normalise and
+    //      store this thread's half row ----
+    float* s_half = reinterpret_cast<float*>(smem + G::kOffP);          // [2][128]
+    s_half[hf * BM + row_l] = l_run;
+    __syncthreads();
+    const float l_tot = l_run + s_half[(hf ^ 1) * BM + row_l];
+    const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
 #pragma unroll
-    for (int c0 = 0; c0 < D; c0 += 32) {
+    for (int c0 = hf * (D / 2); c0 < (hf + 1) * (D / 2); c0 += 32) {
         uint32_t r[32];
         tc::tmem_ld32(tmem_o + lane_sel + c0, r);
         tc::tmem_ld_wait();
