@@ -288,8 +288,8 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
         tc::tc_fence_before();
         __syncthreads();                           // P complete, S(j) consumed, O rescaled, V(j) in place
 
-        // ---- O += P V(j) ----
-        if (tid == 0) {
+        // ---- O += P V(j)  (issued by another warp than Q.K^T, to share the issue work) ----
+        if (tid == NT / 2) {
             tc::tc_fence_after();
             const uint32_t vt = sv + (j & 1) * G::kTileBytes;
 #pragma unroll
