@@ -150,3 +150,32 @@ def test_prefill_argument_checks():
         attn.gqa_prefill(q.float(), k.float(), v.float(), ql, kl, backend="tensorcore")
     empty = attn.gqa_prefill(q[:0], k[:0], v[:0], ql[:0], kl[:0])
     assert empty.shape == (0, 8, 4, 64)
+
+
+@pytest.mark.gpu
+def test_prefill_degenerate_shapes():
+    """No keys at all, a single query row, and query tiles that end inside a 128-row tile."""
+    q, k, v, ql, kl = _case(2, 5, 7, 4, 2, 128, torch.bfloat16, [5, 2], [7, 0])
+    empty_kv = torch.empty(2, 0, 2, 128, dtype=torch.bfloat16, device=DEV)
+    out = attn.gqa_prefill(q, empty_kv, empty_kv, ql, torch.zeros_like(kl))
+    assert out.shape == q.shape and torch.count_nonzero(out) == 0
+    for kernel in ("auto", "mma", "tcgen05", "simt"):
+        got = attn.gqa_prefill(q, k, v, ql, kl, kernel=kernel)
+        _close(got, gqa_oracle.reference_gqa_prefill(q, k, v, ql, kl), torch.bfloat16, kernel)
+        assert torch.count_nonzero(got[1]) == 0          # sequence 1 has no keys
+    args = _case(3, 129, 257, 8, 4, 64, torch.float16, [129, 1, 128], [257, 200, 128], seed=4)
+    want = gqa_oracle.reference_gqa_prefill(*args)
+    for kernel in ("mma", "tcgen05"):
+        _close(attn.gqa_prefill(*args, kernel=kernel), want, torch.float16, kernel)
+
+
+@pytest.mark.gpu
+def test_prefill_kernels_agree_on_a_large_ragged_batch():
+    """tcgen05, mma.sync and the oracle on 16 ragged sequences up to 3000 tokens."""
+    gen = torch.Generator().manual_seed(77)
+    q_lens = torch.randint(1, 3001, (16,), generator=gen).tolist()
+    kv_lens = [n + int(torch.randint(0, 500, (1,), generator=gen)) for n in q_lens]
+    args = _case(16, 3000, 3500, 16, 4, 128, torch.bfloat16, q_lens, kv_lens, seed=78)
+    want = gqa_oracle.reference_gqa_prefill(*args)
+    for kernel in ("tcgen05", "mma"):
+        _close(attn.gqa_prefill(*args, kernel=kernel), want, torch.bfloat16, kernel)
