@@ -19,8 +19,8 @@
 // previous P.V) while the threads exponentiate; P.V(j) is issued as soon as P(j) is in
 // shared memory.  Two CTAs fit per SM (112 KB of shared memory, 256 TMEM columns each).
 //
-// Every mbarrier wait is bounded; a wait that runs out marks the CTA dead (later waits
-// give up at once), raises the status word and the kernel still frees its TMEM.
+// Every mbarrier wait is bounded (one second); a wait that runs out marks the CTA dead (later
+// waits give up at once), raises the status word and the kernel still frees its TMEM.
 #pragma once
 
 #include <type_traits>
@@ -155,7 +155,7 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
     bool alive = true;
 
     auto wait_bar = [&](uint32_t bar, uint32_t parity) {
-        const bool ok = tc::mbar_wait(bar, parity, s_dead ? 16u : (1u << 22));
+        const bool ok = tc::mbar_wait(bar, parity, s_dead ? 1000ull : 1000000000ull);
         if (!ok) {
             s_dead = 1;
             alive = false;
@@ -201,23 +201,22 @@ gqa_prefill_tc_kernel(const PrefillParams p, int* status) {
         float s[HC];
         float mx;
         {
-            uint32_t r[32];
-            tc::tmem_ld32(tmem + (j & 1) * BN + lane_sel + (hf ^ 1) * HC, r);   // the other half
-            tc::tmem_ld_wait();
+            uint32_t r[32], ro[32];
+            tc::tmem_ld32(tmem + (j & 1) * BN + lane_sel + hf * HC, r);          // this thread's half
+            tc::tmem_ld32(tmem + (j & 1) * BN + lane_sel + (hf ^ 1) * HC, ro);   // the other half
+            tc::tmem_ld_wait();                                                   // both in flight together
             const int t_other = j * BN + (hf ^ 1) * HC;
             float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
             if (t_other + HC > my_end) {
 #pragma unroll
                 for (int c = 0; c < HC; ++c)
-                    if (t_other + c >= my_end) r[c] = 0xff800000u;   // -inf
+                    if (t_other + c >= my_end) ro[c] = 0xff800000u;   // -inf
             }
 #pragma unroll
             for (int c = 0; c < HC; c += 4) {
-                a0 = fmaxf(a0, __uint_as_float(r[c])); a1 = fmaxf(a1, __uint_as_float(r[c + 1]));
-                a2 = fmaxf(a2, __uint_as_float(r[c + 2])); a3 = fmaxf(a3, __uint_as_float(r[c + 3]));
+                a0 = fmaxf(a0, __uint_as_float(ro[c])); a1 = fmaxf(a1, __uint_as_float(ro[c + 1]));
+                a2 = fmaxf(a2, __uint_as_float(ro[c + 2])); a3 = fmaxf(a3, __uint_as_float(ro[c + 3]));
             }
-            tc::tmem_ld32(tmem + (j & 1) * BN + lane_sel + hf * HC, r);         // this thread's half
-            tc::tmem_ld_wait();
 #pragma unroll
             for (int c = 0; c < HC; ++c) s[c] = __uint_as_float(r[c]);
             const int t_base = j * BN + hf * HC;

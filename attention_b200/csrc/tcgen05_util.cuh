@@ -18,9 +18,17 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void fence_mbar_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
-// bounded wait: returns false on timeout
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t max_iters = (1u << 22)) {
-    for (uint32_t i = 0; i < max_iters; ++i) {
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait for the completion of the barrier phase with the given parity.  Gives up
+// (returns false) after max_ns nanoseconds of polling, so a lost arrival ends the kernel
+// with an error status instead of hanging the GPU.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_t max_ns = 1000000000ull) {
+    uint64_t start = 0;
+    for (uint32_t i = 0;; ++i) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -28,8 +36,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
         if (done) return true;
+        if ((i & 63u) == 63u) {
+            const uint64_t now = global_timer_ns();
+            if (start == 0) start = now;
+            else if (now - start > max_ns) return false;
+        }
     }
-    return false;
 }
 
 // ---- proxy / tcgen05 fences ----
