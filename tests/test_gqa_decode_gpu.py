@@ -353,3 +353,18 @@ def test_decode_can_be_captured_in_a_cuda_graph_and_replayed():
     graph.replay()
     torch.cuda.synchronize()
     _assert_close(out, _oracle(dq, dk, dv, dt, dl), torch.bfloat16, "second replay")
+
+
+def test_batches_larger_than_the_plan_kernels_block():
+    """More sequences than the plan kernel has threads (its scan runs in several rounds), with
+    empty, one-chunk and many-chunk sequences mixed."""
+    gen = torch.Generator().manual_seed(5)
+    lengths = torch.randint(0, 120, (2500,), generator=gen).tolist()
+    lengths[7] = 700
+    lengths[1999] = 0
+    q, k, v, table, lens = _make_case(lengths, 4, 2, 64, 16, torch.float16, seed=31)
+    args = _cuda(q, k, v, table, lens)
+    want = _oracle(*args)
+    for chunk in (0, 16, 64):
+        _assert_close(attn.gqa_decode(*args, chunk_tokens=chunk), want, torch.float16, f"chunk={chunk}")
+    _assert_close(attn.gqa_decode(*args, kernel="simt", chunk_tokens=32), want, torch.float16, "simt")
