@@ -152,3 +152,81 @@ def algorithmic_bytes(context_lens: torch.Tensor, *, batch: int, q_heads: int, k
     """
     tokens = int(context_lens.to(torch.int64).sum().item())
     return tokens * kv_heads * head_dim * 2 * elem_size + 2 * batch * q_heads * head_dim * elem_size
+
+
+# ---------------------------------------------------------------------------
+# paged latent (MLA) decode workloads
+# ---------------------------------------------------------------------------
+@dataclass(frozen=True)
+class MlaWorkload:
+    name: str
+    batch: int
+    tq: int                # query tokens per sequence (1 = plain decode)
+    heads: int
+    dn: int                # no-rope query width
+    dr: int                # rotated width
+    dc: int                # compressed latent width
+    dv: int                # value width per head
+    page: int
+    dtype: torch.dtype
+    len_lo: int
+    len_hi: int
+    pool_factor: float = 1.25
+
+
+# "DeepSeek-shape" borrows only the published head geometry (128 heads, 512 + 64 wide
+# latent rows); no weights, prompts or datasets are involved.
+MLA_WORKLOADS = {
+    "m1_small_fp32": MlaWorkload("m1_small_fp32", 2, 1, 4, 16, 8, 32, 16, 16, torch.float32, 20, 64),
+    "m2_deepseek_h128_bf16": MlaWorkload("m2_deepseek_h128_bf16", 64, 1, 128, 128, 64, 512, 128, 64,
+                                         torch.bfloat16, 1024, 4096),
+    "m3_deepseek_h16_bf16": MlaWorkload("m3_deepseek_h16_bf16", 128, 1, 16, 128, 64, 512, 128, 64,
+                                        torch.bfloat16, 1024, 8192),
+}
+
+
+def make_mla_case(w: MlaWorkload | str, *, seed: int = 42, device="cpu", lengths=None,
+                  cache_on_device: bool = False):
+    """A dict of tensors for one MLA decode call.
+
+    Draw order with one CPU generator seeded with ``seed``: lengths (unless given), q_nope,
+    q_rope, W_uk / sqrt(Dn), W_uv / sqrt(Dc), the page pool, the page permutation.  The weight
+    scaling follows the reference's benchmark fixtures (benchmarks/bench_attention_primitives.py:52).
+    positions[b, t] = len_b - tq + t, the last tq tokens of each sequence.
+    """
+    if isinstance(w, str):
+        w = MLA_WORKLOADS[w]
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    if lengths is None:
+        lens = torch.randint(w.len_lo, w.len_hi + 1, (w.batch,), generator=gen).to(torch.int32)
+    else:
+        lens = torch.as_tensor(lengths, dtype=torch.int32)
+    q_nope = torch.randn(w.batch, w.tq, w.heads, w.dn, generator=gen)
+    q_rope = torch.randn(w.batch, w.tq, w.heads, w.dr, generator=gen)
+    w_uk = torch.randn(w.heads, w.dn, w.dc, generator=gen) / math.sqrt(w.dn)
+    w_uv = torch.randn(w.heads, w.dv, w.dc, generator=gen) / math.sqrt(w.dc)
+    need = sum((int(n) + w.page - 1) // w.page for n in lens.tolist())
+    pool = max(1, math.ceil(w.pool_factor * need))
+    shape = (pool, w.page, w.dc + w.dr)
+    if cache_on_device:
+        dgen = torch.Generator(device=device).manual_seed(seed)
+        cache = torch.empty(shape, dtype=w.dtype, device=device).normal_(generator=dgen)
+    else:
+        cache = torch.randn(shape, generator=gen).to(w.dtype).to(device)
+    table = build_block_table(lens, w.page, pool, gen)
+    positions = (lens[:, None].to(torch.int64) - w.tq + torch.arange(w.tq)[None, :]).to(torch.int32)
+    to = lambda t: t.to(device=device, dtype=w.dtype).contiguous()   # noqa: E731
+    return {
+        "q_nope": to(q_nope), "q_rope": to(q_rope), "w_uk": to(w_uk), "w_uv": to(w_uv),
+        "cache": cache.contiguous(), "block_table": table.to(device).contiguous(),
+        "lengths": lens.to(device), "positions": positions.to(device).contiguous(),
+    }
+
+
+def mla_algorithmic_bytes(lengths: torch.Tensor, w: MlaWorkload) -> int:
+    """Bytes one latent-attention call must move: every visible cache row once, the absorbed
+    and rotated queries in, the latent output back.  Page tables and split partials are not counted."""
+    es = torch.empty((), dtype=w.dtype).element_size()
+    tokens = int(lengths.to(torch.int64).sum().item())
+    rows = w.batch * w.tq * w.heads
+    return tokens * (w.dc + w.dr) * es + rows * (w.dc + w.dr) * es + rows * w.dc * es

@@ -82,3 +82,18 @@ def load_prefill(name):
     return (from_np(z["q"], dn), from_np(z["k"], dn), from_np(z["v"], dn),
             torch.from_numpy(z["q_lens"].copy()), torch.from_numpy(z["kv_lens"].copy()),
             bool(int(z["causal"])), None if scale < 0 else scale, from_np(z["out"], dn))
+
+
+def mla_cases():
+    return sorted(p.stem for p in GOLDEN_DIR.glob("mla_*.npz"))
+
+
+def load_mla(name):
+    """-> (dict of input tensors incl. optional 'indices', causal, reference_out [B,T,H,Dv])"""
+    z = np.load(GOLDEN_DIR / f"{name}.npz")
+    dn = str(z["dtype"])
+    c = {k: from_np(z[k], dn) for k in ("q_nope", "q_rope", "w_uk", "w_uv", "cache")}
+    for k in ("block_table", "lengths", "positions"):
+        c[k] = torch.from_numpy(z[k].copy())
+    c["indices"] = torch.from_numpy(z["indices"].copy()) if "indices" in z.files else None
+    return c, bool(int(z["causal"])), from_np(z["out"], dn)

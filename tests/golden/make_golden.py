@@ -9,6 +9,8 @@ and the reference's fixture generator ``make_decode_case``
 (benchmarks/data.py:8-43) from that checkout, and writes
 
   full_*.npz   small cases with every input stored next to the reference output
+  prefill_*.npz dense prefill cases, inputs stored in full
+  mla_*.npz    paged latent (MLA) decode cases, inputs stored in full
   seed_*.npz   larger cases: only the generator arguments, a sha256 of the
                regenerated inputs, and the reference output are stored; a test
                regenerates the inputs from the seed, checks the digest, then
@@ -113,7 +115,59 @@ def prefill_cases(ref_root: str) -> None:
         print(name, tuple(out.shape))
 
 
+def mla_cases(ref_root: str) -> None:
+    """Paged MLA decode fixtures.  The reference's oracle ``mla_reference``
+    (attention/reference/mla.py:6-34, ``absorbed=True``) takes dense ``[B,L,*]`` latents, so the
+    pages of each synthetic cache are gathered through the block table here before the call;
+    the fixture stores the paged inputs and the reference output."""
+    sys.path.insert(0, ref_root)
+    from attention.reference.mla import mla_reference
+
+    W = synth.MlaWorkload
+    cases = [
+        # name, workload, lengths, positions override, indices (K or None), all-visible positions, seed
+        ("mla_f32_small", W("g", 2, 1, 4, 16, 8, 32, 16, 16, torch.float32, 0, 0), [64, 37], None, None, False, 11),
+        ("mla_f16_multiquery", W("g", 3, 3, 4, 32, 16, 64, 32, 8, torch.float16, 0, 0), [50, 9, 0],
+         [[47, 48, 49], [2, -1, 8], [0, 1, 2]], None, False, 12),
+        ("mla_f32_sparse", W("g", 2, 2, 3, 16, 8, 32, 16, 4, torch.float32, 0, 0), [30, 21], None, 12, False, 13),
+        ("mla_bf16_wide", W("g", 2, 1, 4, 32, 64, 512, 32, 32, torch.bfloat16, 0, 0), [100, 40], None, None, False, 14),
+        ("mla_bf16_allvisible", W("g", 2, 2, 5, 16, 16, 128, 16, 16, torch.bfloat16, 0, 0), [33, 80], None, None, True, 15),
+    ]
+    for name, w, lens, pos, nk, all_visible, seed in cases:
+        c = synth.make_mla_case(w, seed=seed, lengths=lens)
+        if pos is not None:
+            c["positions"] = torch.tensor(pos, dtype=torch.int32)
+        cap = c["block_table"].shape[1] * w.page
+        ref_pos = torch.full_like(c["positions"], cap) if all_visible else c["positions"]
+        indices = None
+        if nk is not None:
+            gen = torch.Generator().manual_seed(seed + 100)
+            rows = []
+            for b in range(w.batch):
+                for t in range(w.tq):
+                    ix = torch.randperm(cap, generator=gen)[:nk].to(torch.int32)   # unique; some past len
+                    ix[torch.randint(0, nk, (2,), generator=gen)] = -1             # ignored entries
+                    rows.append(ix)
+            indices = torch.stack(rows).view(w.batch, w.tq, nk)
+        used = (c["lengths"].to(torch.int64) + w.page - 1) // w.page
+        safe = torch.where(torch.arange(c["block_table"].shape[1])[None, :] < used[:, None],
+                           c["block_table"].to(torch.int64), torch.zeros((), dtype=torch.int64))
+        dense = c["cache"][safe.reshape(-1)].reshape(w.batch, cap, w.dc + w.dr)
+        out = mla_reference(c["q_nope"], c["q_rope"], dense[..., :w.dc].contiguous(),
+                            dense[..., w.dc:].contiguous(), c["w_uk"], c["w_uv"], ref_pos, c["lengths"],
+                            absorbed=True, indices=indices)
+        arrays = {k: to_np(v) for k, v in c.items()}
+        if indices is not None:
+            arrays["indices"] = to_np(indices)
+        np.savez_compressed(HERE / f"{name}.npz", out=to_np(out), dtype=str(w.dtype).replace("torch.", ""),
+                            causal=np.int64(0 if all_visible else 1), **arrays)
+        print(name, tuple(out.shape))
+
+
 if __name__ == "__main__":
+    mla_cases(sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--") else "/root/reference")
+    if "--mla-only" in sys.argv:
+        sys.exit(0)
     prefill_cases(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
     if "--prefill-only" in sys.argv:
         sys.exit(0)

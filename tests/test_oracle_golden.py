@@ -84,3 +84,58 @@ def test_kv_append_restatement_roundtrip():
         assert torch.equal(k2[phys, t % bs], key[b]) and torch.equal(v2[phys, t % bs], val[b])
     changed = (k2 != k).any(dim=(2, 3)).sum()
     assert changed <= q.shape[0]
+
+
+# ---------------------------------------------------------------------------
+# paged latent (MLA) decode restatements against the reference's mla_reference
+# ---------------------------------------------------------------------------
+from conftest import load_mla, mla_cases  # noqa: E402
+from oracle import mla_oracle  # noqa: E402
+
+
+@pytest.mark.parametrize("name", mla_cases())
+def test_mla_restatement_matches_reference(name):
+    c, causal, want = load_mla(name)
+    got = mla_oracle.reference_mla_decode(c["q_nope"], c["q_rope"], c["cache"], c["block_table"],
+                                          c["lengths"], c["positions"], c["w_uk"], c["w_uv"],
+                                          causal=causal, indices=c["indices"])
+    assert got.dtype == want.dtype and got.shape == want.shape
+    _close(got, want, want.dtype)
+
+
+@pytest.mark.parametrize("name", mla_cases())
+def test_mla_f64_stream_matches_dense_restatement(name):
+    c, causal, _ = load_mla(name)
+    scale = 1.0 / (c["q_nope"].shape[-1] + c["q_rope"].shape[-1]) ** 0.5
+    qa = mla_oracle.reference_mla_project(c["q_nope"], c["w_uk"], True)
+    dense = mla_oracle.reference_mla_latent_attention(qa, c["q_rope"], c["cache"], c["block_table"],
+                                                      c["lengths"], c["positions"], scale=scale,
+                                                      causal=causal, indices=c["indices"])
+    stream = mla_oracle.mla_latent_attention_f64(qa, c["q_rope"], c["cache"], c["block_table"], c["lengths"],
+                                                 c["positions"], scale=scale, causal=causal,
+                                                 indices=c["indices"])
+    _close(torch.from_numpy(stream).to(dense.dtype), dense, dense.dtype)
+
+
+def test_mla_rows_without_visible_tokens_are_zero():
+    c, causal, want = load_mla("mla_f16_multiquery")
+    assert int(c["lengths"][2]) == 0 and int(c["positions"][1, 1]) == -1
+    assert torch.count_nonzero(want[2]) == 0 and torch.count_nonzero(want[1, 1]) == 0
+    got = mla_oracle.reference_mla_decode(c["q_nope"], c["q_rope"], c["cache"], c["block_table"],
+                                          c["lengths"], c["positions"], c["w_uk"], c["w_uv"])
+    assert torch.count_nonzero(got[2]) == 0 and torch.count_nonzero(got[1, 1]) == 0
+
+
+def test_latent_kv_write_restatement():
+    c, _, _ = load_mla("mla_f32_small")
+    cache = c["cache"]
+    dc = c["w_uk"].shape[-1]
+    slots = torch.tensor([5, 0, 17], dtype=torch.int64)
+    lat = torch.randn(3, dc)
+    rope = torch.randn(3, cache.shape[-1] - dc)
+    out = mla_oracle.reference_latent_kv_write(lat, rope, cache, slots)
+    flat = out.view(-1, cache.shape[-1])
+    assert torch.equal(flat[slots, :dc], lat) and torch.equal(flat[slots, dc:], rope)
+    keep = torch.ones(flat.shape[0], dtype=torch.bool)
+    keep[slots] = False
+    assert torch.equal(flat[keep], cache.view(-1, cache.shape[-1])[keep])
