@@ -1,4 +1,5 @@
-"""ctypes binding of the C-ABI library declared in include/gqa_decode_b200.h."""
+"""ctypes binding of the C-ABI library declared in include/gqa_decode_b200.h and
+include/mla_decode_b200.h."""
 
 from __future__ import annotations
 
@@ -9,7 +10,7 @@ from ._paths import LIB_PATH
 
 _P = c_void_p
 
-# name -> (restype, argtypes); mirrors include/gqa_decode_b200.h one to one
+# name -> (restype, argtypes); mirrors the two headers one to one
 SIGNATURES = {
     "gqa_b200_abi_version": (c_int, []),
     "gqa_b200_strerror": (ctypes.c_char_p, [c_int]),
@@ -27,6 +28,18 @@ SIGNATURES = {
     "gqa_b200_prefill": (c_int, [_P] * 6 + [c_int] * 7 + [c_float, c_int, c_int, _P]),
     "gqa_b200_prefill_tc_status": (c_int, [c_int]),
     "gqa_b200_kv_append": (c_int, [_P] * 6 + [c_int] * 4 + [c_int64, c_int, c_int, _P]),
+    # include/mla_decode_b200.h
+    "mla_b200_project": (c_int, [_P] * 3 + [c_int, c_int64] + [c_int] * 4 + [_P]),
+    "mla_b200_latent_kv_write": (c_int, [_P] * 4 + [c_int64, c_int, c_int, c_int, _P]),
+    "mla_b200_attend_workspace_bytes": (c_size_t, [c_int] * 8),
+    "mla_b200_attend": (c_int, [_P] * 8 + [c_int] * 6 + [c_int64, c_int, c_int, c_int, c_float, c_int,
+                                                         _P, c_size_t, _P]),
+    "mla_b200_attend_ex": (c_int, [_P] * 8 + [c_int] * 6 + [c_int64, c_int, c_int, c_int, c_float, c_int,
+                                                            _P, c_size_t, _P, c_int, c_int]),
+    "mla_b200_decode_workspace_bytes": (c_size_t, [c_int] * 8),
+    "mla_b200_decode": (c_int, [_P] * 10 + [c_int] * 8 + [c_int64, c_int, c_int, c_int, c_float, c_int,
+                                                          _P, c_size_t, _P]),
+    "mla_b200_tc_status": (c_int, [c_int]),
 }
 
 _lib = None

@@ -7,3 +7,4 @@ CSRC = PKG / "csrc"
 LIB_DIR = PKG / "_lib"
 LIB_PATH = LIB_DIR / "libgqa_decode_b200.so"
 HEADER = PKG.parent / "include" / "gqa_decode_b200.h"
+MLA_HEADER = PKG.parent / "include" / "mla_decode_b200.h"

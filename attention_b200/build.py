@@ -10,7 +10,7 @@ import subprocess
 import sys
 from pathlib import Path
 
-from ._paths import CSRC, HEADER, LIB_DIR, LIB_PATH
+from ._paths import CSRC, HEADER, LIB_DIR, LIB_PATH, MLA_HEADER
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -27,7 +27,7 @@ def _stale() -> bool:
     if not LIB_PATH.exists():
         return True
     built = LIB_PATH.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [HEADER]
+    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [HEADER, MLA_HEADER]
     return any(d.stat().st_mtime > built for d in deps)
 
 

@@ -440,6 +440,8 @@ const char* gqa_b200_strerror(int code) {
         case GQA_B200_ERR_STATIC_LIMIT:
             return "shape needs more scratch than gqa_b200_decode_static's built-in "
                    "GQA_B200_STATIC_SCRATCH_BYTES; use gqa_b200_decode with a caller workspace";
+        case -32: return "MLA: a width, head count, tq or nk is not positive";   // MLA_B200_ERR_SHAPE
+        case -33: return "MLA: supported latent width dc is [1, 512]";           // MLA_B200_ERR_LATENT_DIM
         default: break;
     }
     if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));

@@ -1,0 +1,271 @@
+// Host side of the paged latent-attention (MLA) decode entry points declared in
+// include/mla_decode_b200.h: argument checks, the static split policy, the
+// workspace layout and the kernel launches.  No allocation, no synchronisation.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+
+#include "../../include/mla_decode_b200.h"
+#include "mla_simt.cuh"
+
+namespace gqa_b200 {
+namespace {
+
+constexpr int kMaxDevices = 64;
+constexpr int kMlaMaxSplits = 32;
+constexpr int kMlaMinTokensPerSplit = 64;
+
+int g_sm_count[kMaxDevices];
+
+cudaError_t sm_count(int* out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (g_sm_count[dev] == 0) {
+        int n = 0;
+        e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+        g_sm_count[dev] = n;
+    }
+    *out = g_sm_count[dev];
+    return cudaSuccess;
+}
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Split count of the SIMT attention kernel: a function of the static shape only
+// (token capacity and CTA count), so that the host never reads a length.  148
+// SMs x 4 resident CTAs is the target; a split never gets fewer than 64 tokens
+// of capacity.
+int simt_auto_splits(long long rows, int heads, int capacity) {
+    const long long base = rows * ((heads + kMlaSimtHeads - 1) / kMlaSimtHeads);
+    const long long target = 148LL * 4;
+    long long s = base > 0 ? (target + base - 1) / base : 1;
+    const long long by_cap = capacity / kMlaMinTokensPerSplit;
+    if (s > by_cap) s = by_cap;
+    if (s > kMlaMaxSplits) s = kMlaMaxSplits;
+    return s < 1 ? 1 : (int)s;
+}
+
+size_t partial_bytes(long long rows, int heads, int dc, int splits) {
+    if (splits <= 1) return 0;
+    const size_t n = (size_t)rows * heads * splits;
+    return align_up(n * 2 * sizeof(float), 256) + align_up(n * dc * sizeof(float), 256);
+}
+
+int check_attend_shape(int dtype, int batch, int tq, int heads, int dc, int dr, long long num_blocks,
+                       int page, int max_pages, int nk) {
+    if (dtype != GQA_B200_F32 && dtype != GQA_B200_F16 && dtype != GQA_B200_BF16) return GQA_B200_ERR_DTYPE;
+    if (batch < 0) return GQA_B200_ERR_BATCH;
+    if (tq < 0 || heads <= 0 || dr <= 0 || nk < 0) return MLA_B200_ERR_SHAPE;
+    if (dc <= 0 || dc > 512) return MLA_B200_ERR_LATENT_DIM;
+    if (num_blocks <= 0 || page <= 0) return GQA_B200_ERR_CACHE_SHAPE;
+    if (max_pages <= 0) return GQA_B200_ERR_MAX_PAGES;
+    if ((long long)batch * tq > 2147483647LL || (long long)page * max_pages > 2147483647LL ||
+        num_blocks > 2147483647LL || (heads + kMlaSimtHeads - 1) / kMlaSimtHeads > 65535)
+        return GQA_B200_ERR_INT32_RANGE;
+    return GQA_B200_OK;
+}
+
+template <typename T>
+int launch_attend_simt(const MlaParams& p, cudaStream_t stream) {
+    const long long rows = (long long)p.batch * p.tq;
+    const size_t smem = ((size_t)kMlaSimtHeads * (p.dc + p.dr) +
+                         (size_t)kMlaSimtWarps * kMlaSimtHeads * p.dc) * sizeof(float);
+    const dim3 grid((unsigned)rows, (unsigned)((p.heads + kMlaSimtHeads - 1) / kMlaSimtHeads),
+                    (unsigned)p.splits);
+    const int dcn = (p.dc + 31) / 32;
+    auto go = [&](auto kernel) -> int {
+        if (smem > 48 * 1024) {
+            if (smem > 200 * 1024) return GQA_B200_ERR_KERNEL;
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        kernel<<<grid, kMlaSimtWarps * 32, smem, stream>>>(p);
+        return (int)cudaGetLastError();
+    };
+    int rc;
+    if (dcn <= 2) rc = go(mla_attend_simt_kernel<T, 2>);
+    else if (dcn <= 4) rc = go(mla_attend_simt_kernel<T, 4>);
+    else if (dcn <= 8) rc = go(mla_attend_simt_kernel<T, 8>);
+    else rc = go(mla_attend_simt_kernel<T, 16>);
+    if (rc != 0) return rc;
+    if (p.splits > 1) {
+        mla_merge_kernel<T><<<(unsigned)(rows * p.heads), 128, 0, stream>>>(p);
+        rc = (int)cudaGetLastError();
+    }
+    return rc;
+}
+
+template <typename T>
+int launch_project(const void* x, const void* w, void* out, long long rows, int heads, int d_in,
+                   int d_out, int absorb, cudaStream_t stream) {
+    const size_t smem = (size_t)kProjRows * d_in * sizeof(float);
+    if (smem > 48 * 1024) return GQA_B200_ERR_KERNEL;
+    const unsigned chunks = (unsigned)((rows + kProjRows - 1) / kProjRows);
+    if (absorb) {
+        const dim3 grid(chunks, (unsigned)((d_out + kProjThreads - 1) / kProjThreads), (unsigned)heads);
+        mla_absorb_kernel<T><<<grid, kProjThreads, smem, stream>>>(
+            static_cast<const T*>(x), static_cast<const T*>(w), static_cast<T*>(out), rows, heads, d_in, d_out);
+    } else {
+        const int per_cta = (kProjThreads / 32) * 8;
+        const dim3 grid(chunks, (unsigned)((d_out + per_cta - 1) / per_cta), (unsigned)heads);
+        mla_value_kernel<T><<<grid, kProjThreads, smem, stream>>>(
+            static_cast<const T*>(x), static_cast<const T*>(w), static_cast<T*>(out), rows, heads, d_in, d_out);
+    }
+    return (int)cudaGetLastError();
+}
+
+template <typename F>
+int by_dtype(int dtype, F&& f) {
+    switch (dtype) {
+        case GQA_B200_F32: return f(float{});
+        case GQA_B200_F16: return f(__half{});
+        case GQA_B200_BF16: return f(__nv_bfloat16{});
+        default: return GQA_B200_ERR_DTYPE;
+    }
+}
+
+}  // namespace
+}  // namespace gqa_b200
+
+using namespace gqa_b200;
+
+extern "C" {
+
+int mla_b200_project(const void* x, const void* w, void* out, int dtype, int64_t rows, int heads,
+                     int d_in, int d_out, int absorb, void* stream) {
+    if (dtype != GQA_B200_F32 && dtype != GQA_B200_F16 && dtype != GQA_B200_BF16) return GQA_B200_ERR_DTYPE;
+    if (rows < 0 || heads <= 0 || d_in <= 0 || d_out <= 0) return MLA_B200_ERR_SHAPE;
+    if (heads > 65535 || (rows + kProjRows - 1) / kProjRows > 2147483647LL) return GQA_B200_ERR_INT32_RANGE;
+    if (rows == 0) return GQA_B200_OK;
+    if (!x || !w || !out) return GQA_B200_ERR_NULL_POINTER;
+    return by_dtype(dtype, [&](auto tag) {
+        return launch_project<decltype(tag)>(x, w, out, rows, heads, d_in, d_out, absorb,
+                                             static_cast<cudaStream_t>(stream));
+    });
+}
+
+int mla_b200_latent_kv_write(const void* latent, const void* rope, void* cache, const int64_t* slots,
+                             int64_t n, int dc, int dr, int dtype, void* stream) {
+    if (dtype != GQA_B200_F32 && dtype != GQA_B200_F16 && dtype != GQA_B200_BF16) return GQA_B200_ERR_DTYPE;
+    if (n < 0 || dc <= 0 || dr <= 0) return MLA_B200_ERR_SHAPE;
+    if (n > 2147483647LL) return GQA_B200_ERR_INT32_RANGE;
+    if (n == 0) return GQA_B200_OK;
+    if (!latent || !rope || !cache || !slots) return GQA_B200_ERR_NULL_POINTER;
+    return by_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        mla_cache_write_kernel<T><<<(unsigned)n, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const T*>(latent), static_cast<const T*>(rope), static_cast<T*>(cache), slots, dc, dr);
+        return (int)cudaGetLastError();
+    });
+}
+
+size_t mla_b200_attend_workspace_bytes(int batch, int tq, int heads, int dc, int dr, int page,
+                                       int max_pages, int nk) {
+    if (check_attend_shape(GQA_B200_F32, batch, tq, heads, dc, dr, 1, page, max_pages, nk) != 0) return 0;
+    const long long rows = (long long)batch * tq;
+    const int capacity = nk > 0 ? nk : page * max_pages;
+    const size_t simt = partial_bytes(rows, heads, dc, simt_auto_splits(rows, heads, capacity));
+    return simt > 256 ? simt : 256;
+}
+
+int mla_b200_attend_ex(const void* q_absorbed, const void* q_rope, const void* cache,
+                       const int32_t* block_table, const int32_t* lengths, const int32_t* positions,
+                       const int32_t* indices, void* out, int dtype, int batch, int tq, int heads,
+                       int dc, int dr, int64_t num_blocks, int page, int max_pages, int nk,
+                       float scale, int causal, void* workspace, size_t workspace_bytes, void* stream,
+                       int kernel, int splits) {
+    int rc = check_attend_shape(dtype, batch, tq, heads, dc, dr, num_blocks, page, max_pages, nk);
+    if (rc != 0) return rc;
+    if (!(scale > 0.f) || !std::isfinite(scale)) return GQA_B200_ERR_SCALE;
+    if (splits < 0 || splits > 65535) return GQA_B200_ERR_SPLITS;
+    if (batch == 0 || tq == 0) return GQA_B200_OK;
+    if (!q_absorbed || !q_rope || !cache || !block_table || !lengths || !positions || !out)
+        return GQA_B200_ERR_NULL_POINTER;
+    if (indices && nk <= 0) return MLA_B200_ERR_SHAPE;
+    if (kernel != MLA_B200_KERNEL_AUTO && kernel != MLA_B200_KERNEL_SIMT) return GQA_B200_ERR_KERNEL;
+
+    const long long rows = (long long)batch * tq;
+    const int capacity = indices ? nk : page * max_pages;
+    MlaParams p{};
+    p.q = q_absorbed; p.qr = q_rope; p.cache = cache; p.table = block_table; p.lens = lengths;
+    p.pos = positions; p.indices = indices; p.out = out;
+    p.num_blocks = num_blocks;
+    p.batch = batch; p.tq = tq; p.heads = heads; p.dc = dc; p.dr = dr; p.page = page;
+    p.max_pages = max_pages; p.nk = indices ? nk : 0; p.causal = causal ? 1 : 0;
+    p.scale_log2 = scale * kLog2e;
+    p.splits = splits > 0 ? splits : simt_auto_splits(rows, heads, capacity);
+    if (p.splits > 1) {
+        const size_t need = partial_bytes(rows, heads, dc, p.splits);
+        if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < need)
+            return GQA_B200_ERR_WORKSPACE;
+        const size_t n = (size_t)rows * heads * p.splits;
+        p.part_ml = static_cast<float*>(workspace);
+        p.part_acc = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(n * 2 * sizeof(float), 256));
+    }
+    return by_dtype(dtype, [&](auto tag) {
+        return launch_attend_simt<decltype(tag)>(p, static_cast<cudaStream_t>(stream));
+    });
+}
+
+int mla_b200_attend(const void* q_absorbed, const void* q_rope, const void* cache,
+                    const int32_t* block_table, const int32_t* lengths, const int32_t* positions,
+                    const int32_t* indices, void* out, int dtype, int batch, int tq, int heads, int dc,
+                    int dr, int64_t num_blocks, int page, int max_pages, int nk, float scale,
+                    int causal, void* workspace, size_t workspace_bytes, void* stream) {
+    return mla_b200_attend_ex(q_absorbed, q_rope, cache, block_table, lengths, positions, indices, out,
+                              dtype, batch, tq, heads, dc, dr, num_blocks, page, max_pages, nk, scale,
+                              causal, workspace, workspace_bytes, stream, MLA_B200_KERNEL_AUTO, 0);
+}
+
+static size_t stage_bytes(int batch, int tq, int heads, int dc) {
+    return align_up((size_t)batch * tq * heads * dc * 4, 256);   // sized for fp32 elements
+}
+
+size_t mla_b200_decode_workspace_bytes(int batch, int tq, int heads, int dc, int dr, int page,
+                                       int max_pages, int nk) {
+    const size_t attend = mla_b200_attend_workspace_bytes(batch, tq, heads, dc, dr, page, max_pages, nk);
+    if (attend == 0) return 0;
+    return 2 * stage_bytes(batch, tq, heads, dc) + attend;
+}
+
+int mla_b200_decode(const void* q_nope, const void* q_rope, const void* cache,
+                    const int32_t* block_table, const int32_t* lengths, const int32_t* positions,
+                    const void* w_uk, const void* w_uv, const int32_t* indices, void* out, int dtype,
+                    int batch, int tq, int heads, int dn, int dr, int dc, int dv, int64_t num_blocks,
+                    int page, int max_pages, int nk, float scale, int causal, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+    int rc = check_attend_shape(dtype, batch, tq, heads, dc, dr, num_blocks, page, max_pages, nk);
+    if (rc != 0) return rc;
+    if (dn <= 0 || dv <= 0) return MLA_B200_ERR_SHAPE;
+    if (!(scale > 0.f) || !std::isfinite(scale)) return GQA_B200_ERR_SCALE;
+    if (batch == 0 || tq == 0) return GQA_B200_OK;
+    if (!q_nope || !w_uk || !w_uv || !out) return GQA_B200_ERR_NULL_POINTER;
+    const size_t stage = stage_bytes(batch, tq, heads, dc);
+    const size_t need = mla_b200_decode_workspace_bytes(batch, tq, heads, dc, dr, page, max_pages, nk);
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < need)
+        return GQA_B200_ERR_WORKSPACE;
+    char* ws = static_cast<char*>(workspace);
+    void* q_abs = ws;
+    void* latent = ws + stage;
+    const int64_t rows = (int64_t)batch * tq;
+    rc = mla_b200_project(q_nope, w_uk, q_abs, dtype, rows, heads, dn, dc, 1, stream);
+    if (rc != 0) return rc;
+    rc = mla_b200_attend(q_abs, q_rope, cache, block_table, lengths, positions, indices, latent, dtype,
+                         batch, tq, heads, dc, dr, num_blocks, page, max_pages, nk, scale, causal,
+                         ws + 2 * stage, workspace_bytes - 2 * stage, stream);
+    if (rc != 0) return rc;
+    return mla_b200_project(latent, w_uv, out, dtype, rows, heads, dc, dv, 0, stream);
+}
+
+int mla_b200_tc_status(int reset) {
+    (void)reset;
+    return 0;
+}
+
+}  // extern "C"

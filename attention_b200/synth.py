@@ -230,3 +230,10 @@ def mla_algorithmic_bytes(lengths: torch.Tensor, w: MlaWorkload) -> int:
     tokens = int(lengths.to(torch.int64).sum().item())
     rows = w.batch * w.tq * w.heads
     return tokens * (w.dc + w.dr) * es + rows * (w.dc + w.dr) * es + rows * w.dc * es
+
+
+def scaled_mla(w: MlaWorkload | str, **changes) -> MlaWorkload:
+    """A copy of an MLA workload with some fields replaced."""
+    if isinstance(w, str):
+        w = MLA_WORKLOADS[w]
+    return replace(w, **changes)

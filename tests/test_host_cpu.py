@@ -9,14 +9,14 @@ import torch
 
 import attention_b200 as attn
 from attention_b200 import _cabi, sharding, synth
-from attention_b200._paths import HEADER
+from attention_b200._paths import HEADER, MLA_HEADER
 
 ROOT = Path(__file__).resolve().parents[1]
 
 
 def _declared_symbols():
-    text = HEADER.read_text()
-    return re.findall(r"GQA_B200_API\s+[\w\s\*]+?\b(gqa_b200_\w+)\s*\(", text)
+    text = HEADER.read_text() + MLA_HEADER.read_text()
+    return re.findall(r"GQA_B200_API\s+[\w\s\*]+?\b((?:gqa|mla)_b200_\w+)\s*\(", text)
 
 
 def test_library_loads_and_exports_every_declared_symbol():
@@ -31,8 +31,8 @@ def test_library_loads_and_exports_every_declared_symbol():
 
 
 def test_strerror_covers_every_status_code():
-    text = HEADER.read_text()
-    codes = [int(c) for c in re.findall(r"#define GQA_B200_ERR_\w+\s+\((-\d+)\)", text)]
+    text = HEADER.read_text() + MLA_HEADER.read_text()
+    codes = [int(c) for c in re.findall(r"#define (?:GQA|MLA)_B200_ERR_\w+\s+\((-\d+)\)", text)]
     assert codes and len(set(codes)) == len(codes)
     for c in codes:
         assert "unknown" not in _cabi.strerror(c)
