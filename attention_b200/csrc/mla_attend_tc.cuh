@@ -1,0 +1,435 @@
+// Paged latent attention (MLA decode) on the 5th-generation tensor cores: tcgen05.mma with
+// TMEM accumulators, run by a pair of CTAs (a cluster of two) that split the 576-wide cache
+// row between them.  fp16 / bf16, dc = 512, dr = 64, dense attention.
+//
+// Why a pair.  With 128 query rows (heads x query tokens of one sequence) the output
+// accumulator is 128 x 512 fp32 = all 512 TMEM columns of an SM, leaving no room for scores.
+// So the row is cut at column 256:
+//   rank 0 : latent columns   0..255                    (4 blocks of 64 columns = 128 bytes)
+//   rank 1 : latent columns 256..511 + the 64 rotated   (5 blocks)
+// Each CTA loads only its own blocks of every cache row (so every byte is read once by the
+// pair), and those same blocks serve both contractions:
+//   S_r[128 x 32]  = Q_r[128 x 64 nb] . C_r[32 x 64 nb]^T     partial scores over its columns
+//   O_r[128 x 256] += P[128 x 32] . C_r[32 x 256]             its half of the latent output
+// The full scores are S_0 + S_1: every thread sends its partial scores to the peer CTA through
+// distributed shared memory and adds what it receives, so both CTAs hold the same scores bit
+// for bit (a + b == b + a) and take the same softmax decisions without further talk.
+//
+// Per CTA: Q_r (80 KB), a five-stage ring of 32-token tiles (20 KB each, 16-byte cp.async
+// with the page lookup per row), the P tile, and the 16 KB landing buffer for the peer's
+// partial scores: 212 KB, one CTA per SM.  TMEM: three score buffers of 32 columns and 256
+// columns of output.  Tiles are loaded four ahead, Q.C^T is issued two tiles ahead of the
+// softmax, P.C is issued as soon as P is in shared memory.
+//
+// Hand-offs (mbarriers; every wait is time-bounded, a wait that runs out marks the CTA dead,
+// raises the status word, and the CTA still walks the protocol to the end so that its peer is
+// never left waiting and no CTA exits while the other may still write into its memory):
+//   bar_s[3]   tcgen05.commit   partial scores of a tile are in TMEM
+//   bar_pv     tcgen05.commit   P.C of a tile is done: its stage, the P tile and O are free
+//   bar_x      256 remote arrivals   the peer's partial scores of a tile have landed here
+//   bar_free   256 remote arrivals   the peer has consumed what this CTA sent it
+#pragma once
+
+#include <type_traits>
+
+#include "gqa_common.cuh"
+#include "gqa_decode_mma.cuh"
+#include "mla_simt.cuh"
+#include "tcgen05_util.cuh"
+
+namespace gqa_b200 {
+
+constexpr int kMlaTcRows = 128;        // query rows (token x head) per CTA pair
+constexpr int kMlaTcBN = 32;           // tokens per tile
+constexpr int kMlaTcThreads = 256;
+constexpr int kMlaTcStages = 5;
+constexpr int kMlaTcAhead = 4;         // tiles loaded ahead of the softmax
+constexpr int kMlaTcSBufs = 3;
+constexpr int kMlaTcTmemCols = 512;
+constexpr int kMlaTcDc = 512;
+constexpr int kMlaTcDr = 64;
+constexpr int kMlaTcWidth = kMlaTcDc + kMlaTcDr;
+
+struct MlaTcGeom {
+    static constexpr int kBlocks = 5;                                   // 128-byte column blocks (rank 1)
+    static constexpr int kQBlockBytes = kMlaTcRows * 128;               // 16 KB
+    static constexpr int kQBytes = kBlocks * kQBlockBytes;              // 80 KB
+    static constexpr int kTileBlockBytes = kMlaTcBN * 128;              // 4 KB
+    static constexpr int kStageBytes = kBlocks * kTileBlockBytes;       // 20 KB
+    static constexpr int kPBytes = kMlaTcRows * 128;                    // 16 KB (64 of 128 bytes per row used)
+    static constexpr int kXBytes = kMlaTcRows * kMlaTcBN * 4;           // 16 KB
+    static constexpr int kOffK = kQBytes;
+    static constexpr int kOffP = kOffK + kMlaTcStages * kStageBytes;
+    static constexpr int kOffX = kOffP + kPBytes;
+    static constexpr int kSmemBytes = kOffX + kXBytes;                  // 217088
+};
+
+namespace tc {
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// address of the same shared-memory location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d)
+                 : "memory");
+}
+// mbar_wait with cluster-scope acquire: orders the peer CTA's stores before the reads that follow.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, uint64_t max_ns) {
+    uint64_t start = 0;
+    for (uint32_t i = 0;; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        if ((i & 63u) == 63u) {
+            const uint64_t now = global_timer_ns();
+            if (start == 0) start = now;
+            else if (now - start > max_ns) return false;
+        }
+    }
+}
+}  // namespace tc
+
+// grid (2 * chunks, row tiles, batch), cluster (2, 1, 1).  p.splits = chunks per sequence
+// (partials when > 1), p.chunk_tokens = tokens per chunk, p.page_shift = log2(page) or -1.
+template <typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMlaTcThreads, 1)
+mla_attend_tc_kernel(const MlaParams p, int* status) {
+    using G = MlaTcGeom;
+    using Ops = MmaOps<T>;
+    constexpr int BM = kMlaTcRows, BN = kMlaTcBN, NT = kMlaTcThreads;
+    constexpr int NS = kMlaTcStages, LA = kMlaTcAhead, NSB = kMlaTcSBufs;
+    constexpr int AB_TYPE = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+    constexpr int HC = BN / 2;                       // score columns per thread
+
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ __align__(8) uint64_t s_bar[NSB + 3]; // S ready x3, P.C done, peer scores landed, peer consumed
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_dead;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quad = warp & 3, hf = warp >> 2;       // TMEM lane quadrant, column half
+    const int row_l = quad * 32 + lane;              // this thread's row of the 128-row tile
+    const uint32_t rank = tc::cluster_ctarank(), peer = rank ^ 1u;
+    const int chunk = blockIdx.x >> 1, b = blockIdx.z;
+    const int R = p.tq * p.heads;                    // query rows of one sequence
+    const int g0 = blockIdx.y * BM, g = g0 + row_l;
+    const int nb = rank ? 5 : 4;                     // 128-byte blocks this CTA owns
+    const int col0 = rank ? 256 : 0;                 // first cache column this CTA owns
+
+    int end_max = 0;
+    for (int t = g0 / p.heads; t <= (min(R, g0 + BM) - 1) / p.heads; ++t) end_max = max(end_max, mla_row_end(p, b, t));
+    const int my_end = g < R ? mla_row_end(p, b, g / p.heads) : 0;
+    const int t0 = chunk * p.chunk_tokens;
+    const int t1 = min(end_max, t0 + p.chunk_tokens);
+    const int n_tiles = t1 > t0 ? (t1 - t0 + BN - 1) / BN : 0;
+    const long long grow = (long long)b * R + g;     // global query row
+    T* op = reinterpret_cast<T*>(p.out);
+
+    if (n_tiles == 0) {                              // nothing visible in this chunk (both CTAs agree)
+        if (g < R) {
+            if (p.splits > 1) {
+                if (rank == 0 && hf == 0) {
+                    p.part_ml[(grow * p.splits + chunk) * 2] = -INFINITY;
+                    p.part_ml[(grow * p.splits + chunk) * 2 + 1] = 0.f;
+                }
+            } else {
+                uint4* dst = reinterpret_cast<uint4*>(op + grow * kMlaTcDc + col0 + hf * 128);
+#pragma unroll
+                for (int c = 0; c < 16; ++c) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        return;
+    }
+
+    const uint32_t s_base = tc::smem_u32(smem);
+    if (s_base & 1023u) {                            // the swizzled tiles need a 1024-byte aligned base
+        if (tid == 0 && status) atomicExch(status, 3);
+        return;
+    }
+    const uint32_t sq = s_base, sk = s_base + G::kOffK, sp = s_base + G::kOffP, sx = s_base + G::kOffX;
+    const uint32_t bar_s0 = tc::smem_u32(&s_bar[0]);
+    const uint32_t bar_pv = tc::smem_u32(&s_bar[NSB]);
+    const uint32_t bar_x = tc::smem_u32(&s_bar[NSB + 1]);
+    const uint32_t bar_free = tc::smem_u32(&s_bar[NSB + 2]);
+    const uint32_t peer_sx = tc::map_to_cta(sx, peer);
+    const uint32_t peer_bar_x = tc::map_to_cta(bar_x, peer);
+    const uint32_t peer_bar_free = tc::map_to_cta(bar_free, peer);
+
+    if (warp == 0) { tc::tmem_alloc(tc::smem_u32(&s_tmem), kMlaTcTmemCols); tc::tmem_relinquish(); }
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < NSB; ++i) tc::mbar_init(bar_s0 + i * 8, 1);
+        tc::mbar_init(bar_pv, 1);
+        tc::mbar_init(bar_x, NT);
+        tc::mbar_init(bar_free, NT);
+        tc::fence_mbar_init();
+        s_dead = 0;
+    }
+
+    // ---- asynchronous copies into swizzled tiles: [64-column block][row][128 B] ----
+    const int cpr = nb * 8;                          // 16-byte chunks of a row that this CTA owns
+    {
+        const T* qa = reinterpret_cast<const T*>(p.q);
+        const T* qr = reinterpret_cast<const T*>(p.qr);
+        for (int i = tid; i < BM * cpr; i += NT) {
+            const int row = i / cpr, c = i - row * cpr;
+            const bool valid = g0 + row < R;
+            const long long gr = (long long)b * R + (valid ? g0 + row : 0);
+            const int col = col0 + c * 8;
+            const T* src = col < kMlaTcDc ? qa + gr * kMlaTcDc + col : qr + gr * kMlaTcDr + (col - kMlaTcDc);
+            cp_async16<0>(sq + (c >> 3) * G::kQBlockBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4), src,
+                          valid ? 16 : 0, 0);
+        }
+    }
+    const char* cache = reinterpret_cast<const char*>(p.cache);
+    const int32_t* trow = p.table + (long long)b * p.max_pages;
+    const int last_block = (int)(p.num_blocks - 1);
+    auto load_tile = [&](int j) {                    // tile j of this chunk into stage j % NS
+        const uint32_t st = sk + (j % NS) * G::kStageBytes;
+        for (int i = tid; i < BN * cpr; i += NT) {
+            const int row = i / cpr, c = i - row * cpr;
+            const int tok = t0 + j * BN + row;
+            const bool valid = tok < t1;
+            const char* src = cache;
+            if (valid) {
+                const int pg = p.page_shift >= 0 ? tok >> p.page_shift : tok / p.page;
+                const int slot = tok - pg * p.page;
+                // a page id outside the pool (a caller error) is clamped instead of faulting
+                const long long phys = min(max(__ldg(trow + pg), 0), last_block);
+                src = cache + ((phys * p.page + slot) * kMlaTcWidth + col0 + c * 8) * 2;
+            }
+            cp_async16<0>(st + (c >> 3) * G::kTileBlockBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4), src,
+                          valid ? 16 : 0, 0);
+        }
+    };
+    load_tile(0);                                    // rides in the same group as Q
+    cp_async_commit();
+#pragma unroll
+    for (int j = 1; j < LA; ++j) {
+        if (j < n_tiles) load_tile(j);
+        cp_async_commit();
+    }
+
+    const int my_stop = min(my_end, t1);             // this row sees tokens [t0, my_stop) of the chunk
+    float m_run = -INFINITY, l_run = 0.f;
+    const uint32_t idesc_s = tc::idesc_f16(BM, BN, AB_TYPE);
+    const uint32_t idesc_o = tc::idesc_f16(BM, 256, AB_TYPE) | tc::kIdescBMnMajor;
+    const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+    bool alive = true;
+
+    auto timed_out = [&]() {
+        s_dead = 1;
+        alive = false;
+        if (status) atomicExch(status, 2);
+    };
+    auto wait_bar = [&](uint32_t bar, uint32_t parity) {
+        if (!tc::mbar_wait(bar, parity, s_dead ? 1000ull : 1000000000ull)) timed_out();
+    };
+    auto wait_bar_cluster = [&](uint32_t bar, uint32_t parity) {
+        if (!tc::mbar_wait_cluster(bar, parity, s_dead ? 1000ull : 1000000000ull)) timed_out();
+    };
+
+    cp_async_wait<1>();                              // Q and tiles 0 .. LA-2 have landed
+    tc::fence_async_smem();
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::cluster_sync_all();                          // both CTAs' barriers exist before any remote arrival
+    tc::tc_fence_after();
+    const uint32_t tmem = s_tmem;
+    const uint32_t tmem_o = tmem + NSB * BN;
+
+    // S_r(j) = Q_r C_r(j)^T into score buffer j % NSB (one thread)
+    auto issue_qk = [&](int j) {
+        const uint32_t st = sk + (j % NS) * G::kStageBytes;
+        const uint32_t d = tmem + (j % NSB) * BN;
+        for (int blk = 0; blk < nb; ++blk) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint64_t da = tc::smem_desc_sw128_kmajor(sq + blk * G::kQBlockBytes + k * 32);
+                const uint64_t db = tc::smem_desc_sw128_kmajor(st + blk * G::kTileBlockBytes + k * 32);
+                tc::mma_f16_ss(d, da, db, idesc_s, (blk | k) ? 1u : 0u);
+            }
+        }
+        tc::mma_commit(bar_s0 + (j % NSB) * 8);
+    };
+    // O_r += P C_r(j): the first four blocks of the stage, as an MN-major operand (one thread)
+    auto issue_pv = [&](int j) {
+        const uint32_t st = sk + (j % NS) * G::kStageBytes;
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k) {
+            const uint64_t da = tc::smem_desc_sw128_kmajor(sp + k * 32);
+            const uint64_t db = tc::smem_desc_sw128_mnmajor(st + k * 2048, G::kTileBlockBytes);
+            tc::mma_f16_ss(tmem_o, da, db, idesc_o, (j | k) ? 1u : 0u);
+        }
+        tc::mma_commit(bar_pv);
+    };
+
+    if (tid == 0) {
+        issue_qk(0);
+        if (n_tiles > 1) issue_qk(1);
+    }
+
+    for (int j = 0; j < n_tiles; ++j) {
+        // ---- this CTA's partial scores of tile j ----
+        wait_bar(bar_s0 + (j % NSB) * 8, (j / NSB) & 1);
+        tc::tc_fence_after();
+        uint32_t r[32];
+        tc::tmem_ld32(tmem + (j % NSB) * BN + lane_sel, r);
+        tc::tmem_ld_wait();
+        // ---- send this thread's 16 columns to the peer (once it has consumed the previous tile) ----
+        if (j > 0) wait_bar_cluster(bar_free, (j - 1) & 1);
+#pragma unroll
+        for (int q4 = 0; q4 < HC / 4; ++q4) {        // (register arrays are indexed statically: select by hf)
+            const int lo = q4 * 4, hi = HC + q4 * 4;
+            tc::st_cluster_v4(peer_sx + ((hf * (HC / 4) + q4) * BM + row_l) * 16, hf ? r[hi] : r[lo],
+                              hf ? r[hi + 1] : r[lo + 1], hf ? r[hi + 2] : r[lo + 2], hf ? r[hi + 3] : r[lo + 3]);
+        }
+        tc::mbar_arrive_remote(peer_bar_x);
+        // tile j+2 landed before the barrier that ended iteration j-1; its score buffer was read in j-1
+        if (tid == 0 && j + 2 < n_tiles) issue_qk(j + 2);
+
+        // ---- full scores = mine + the peer's ----
+        wait_bar_cluster(bar_x, j & 1);
+        float s[BN];
+#pragma unroll
+        for (int c4 = 0; c4 < BN / 4; ++c4) {
+            uint32_t x0, x1, x2, x3;
+            asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3)
+                         : "r"(sx + (c4 * BM + row_l) * 16) : "memory");
+            s[c4 * 4 + 0] = __uint_as_float(r[c4 * 4 + 0]) + __uint_as_float(x0);
+            s[c4 * 4 + 1] = __uint_as_float(r[c4 * 4 + 1]) + __uint_as_float(x1);
+            s[c4 * 4 + 2] = __uint_as_float(r[c4 * 4 + 2]) + __uint_as_float(x2);
+            s[c4 * 4 + 3] = __uint_as_float(r[c4 * 4 + 3]) + __uint_as_float(x3);
+        }
+        tc::mbar_arrive_remote(peer_bar_free);       // the peer may overwrite the landing buffer
+        const int tok0 = t0 + j * BN;
+        if (tok0 + BN > my_stop) {
+#pragma unroll
+            for (int c = 0; c < BN; ++c)
+                if (tok0 + c >= my_stop) s[c] = -INFINITY;
+        }
+        float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < BN; c += 4) {
+            a0 = fmaxf(a0, s[c]); a1 = fmaxf(a1, s[c + 1]); a2 = fmaxf(a2, s[c + 2]); a3 = fmaxf(a3, s[c + 3]);
+        }
+        const float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * p.scale_log2;
+        const bool need = mx > m_run + kRescaleSlack;
+        float alpha = 1.f;
+        if (need) {
+            const float mn = fmaxf(m_run, mx);
+            alpha = m_run == -INFINITY ? 0.f : fast_exp2(m_run - mn);
+            m_run = mn;
+            l_run *= alpha;
+        }
+        const float ref = m_run == -INFINITY ? 0.f : m_run;
+        uint32_t pw[HC / 2];
+        {
+            float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+            for (int c = 0; c < HC; c += 2) {
+                const float p0 = fast_exp2(fmaf(hf ? s[HC + c] : s[c], p.scale_log2, -ref));
+                const float p1 = fast_exp2(fmaf(hf ? s[HC + c + 1] : s[c + 1], p.scale_log2, -ref));
+                ps0 += p0; ps1 += p1;
+                pw[c / 2] = Ops::pack(p0, p1);
+            }
+            l_run += ps0 + ps1;                      // this thread's half of the row sum
+        }
+
+        // ---- P.C(j-1) is done: its stage, the P tile and O may be touched ----
+        if (j > 0) wait_bar(bar_pv, (j - 1) & 1);
+        tc::tc_fence_after();
+        if (j + LA < n_tiles) load_tile(j + LA);     // into the stage tile j-1 used
+        cp_async_commit();
+        if (j > 0 && __any_sync(0xffffffffu, need)) {   // warp-uniform: TMEM ld/st are collective
+#pragma unroll
+            for (int c0 = hf * 128; c0 < (hf + 1) * 128; c0 += 32) {
+                uint32_t o[32];
+                tc::tmem_ld32(tmem_o + lane_sel + c0, o);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+                tc::tmem_st32(tmem_o + lane_sel + c0, o);
+            }
+            tc::tmem_st_wait();
+        }
+#pragma unroll
+        for (int c8 = 0; c8 < HC / 8; ++c8) {
+            const int ch = hf * (HC / 8) + c8;
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(sp + row_l * 128 + ((ch ^ (row_l & 7)) << 4)),
+                         "r"(pw[c8 * 4 + 0]), "r"(pw[c8 * 4 + 1]), "r"(pw[c8 * 4 + 2]), "r"(pw[c8 * 4 + 3])
+                         : "memory");
+        }
+        cp_async_wait<1>();                          // tiles up to j + LA - 1 have landed (this thread's part)
+        tc::fence_async_smem();
+        tc::tc_fence_before();
+        __syncthreads();
+        if (tid == NT / 2) {
+            tc::tc_fence_after();
+            issue_pv(j);
+        }
+    }
+    wait_bar(bar_pv, (n_tiles - 1) & 1);
+    tc::tc_fence_after();
+
+    // ---- row sum = the two halves (exchanged through the idle P tile); store ----
+    float* s_half = reinterpret_cast<float*>(smem + G::kOffP);          // [2][128]
+    s_half[hf * BM + row_l] = l_run;
+    __syncthreads();
+    const float l_tot = l_run + s_half[(hf ^ 1) * BM + row_l];
+    const bool final_out = p.splits == 1;
+    const float inv = final_out ? (l_tot > 0.f ? 1.f / l_tot : 0.f) : 1.f;
+    float* pacc = final_out ? nullptr : p.part_acc + (grow * p.splits + chunk) * kMlaTcDc + col0;
+#pragma unroll
+    for (int c0 = hf * 128; c0 < (hf + 1) * 128; c0 += 32) {
+        uint32_t o[32];
+        tc::tmem_ld32(tmem_o + lane_sel + c0, o);
+        tc::tmem_ld_wait();
+        if (g < R && alive) {
+            if (final_out) {
+                uint4* dst = reinterpret_cast<uint4*>(op + grow * kMlaTcDc + col0 + c0);
+#pragma unroll
+                for (int c8 = 0; c8 < 4; ++c8) {
+                    uint4 v;
+                    v.x = Ops::pack(__uint_as_float(o[c8 * 8 + 0]) * inv, __uint_as_float(o[c8 * 8 + 1]) * inv);
+                    v.y = Ops::pack(__uint_as_float(o[c8 * 8 + 2]) * inv, __uint_as_float(o[c8 * 8 + 3]) * inv);
+                    v.z = Ops::pack(__uint_as_float(o[c8 * 8 + 4]) * inv, __uint_as_float(o[c8 * 8 + 5]) * inv);
+                    v.w = Ops::pack(__uint_as_float(o[c8 * 8 + 6]) * inv, __uint_as_float(o[c8 * 8 + 7]) * inv);
+                    dst[c8] = v;
+                }
+            } else {
+                uint4* dst = reinterpret_cast<uint4*>(pacc + c0);
+#pragma unroll
+                for (int c4 = 0; c4 < 8; ++c4) dst[c4] = make_uint4(o[c4 * 4], o[c4 * 4 + 1], o[c4 * 4 + 2], o[c4 * 4 + 3]);
+            }
+        }
+    }
+    if (!final_out && g < R && alive && rank == 0 && hf == 0) {
+        p.part_ml[(grow * p.splits + chunk) * 2] = m_run;
+        p.part_ml[(grow * p.splits + chunk) * 2 + 1] = l_tot;
+    }
+    cp_async_wait<0>();
+    tc::tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(tmem, kMlaTcTmemCols);
+    tc::cluster_sync_all();                          // neither CTA leaves while the other may still signal it
+}
+
+}  // namespace gqa_b200

@@ -9,6 +9,7 @@
 #include <cstdint>
 
 #include "../../include/mla_decode_b200.h"
+#include "mla_attend_tc.cuh"
 #include "mla_simt.cuh"
 
 namespace gqa_b200 {
@@ -36,6 +37,46 @@ cudaError_t sm_count(int* out) {
 }
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Status word of the tensor-core attention kernel: 0 ok, 2 = a bounded wait ran out, 3 = the
+// dynamic shared memory base was not 1024-byte aligned.  Read with mla_b200_tc_status.
+__device__ int g_mla_tc_status;
+int* g_mla_tc_status_ptr[kMaxDevices];
+bool g_mla_tc_ready[kMaxDevices][2];
+
+cudaError_t mla_tc_status_address(int** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (!g_mla_tc_status_ptr[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_mla_tc_status);
+        if (e != cudaSuccess) return e;
+        g_mla_tc_status_ptr[dev] = static_cast<int*>(ptr);
+    }
+    *out = g_mla_tc_status_ptr[dev];
+    return cudaSuccess;
+}
+
+// Split of the tensor-core kernel: chunks of equal token count, a function of the static
+// shape only.  Starting from one chunk per sequence, the chunk is halved (not below 256
+// tokens) until there are at least two CTA pairs of work per pair of SMs.
+void tc_chunking(long long units, int capacity, int sm_pairs, int* chunk_tokens, int* splits) {
+    int chunk = (capacity + kMlaTcBN - 1) / kMlaTcBN * kMlaTcBN;
+    auto count = [&](int c) { return (capacity + c - 1) / c; };
+    while (chunk > 256 && units * count(chunk) < 2LL * sm_pairs) {
+        int half = (chunk / 2 + kMlaTcBN - 1) / kMlaTcBN * kMlaTcBN;
+        chunk = half < 256 ? 256 : half;
+    }
+    while (count(chunk) > 64) chunk *= 2;
+    *chunk_tokens = chunk;
+    *splits = count(chunk);
+}
+
+bool tc_eligible(int dtype, int dc, int dr, const void* indices) {
+    return (dtype == GQA_B200_F16 || dtype == GQA_B200_BF16) && dc == kMlaTcDc && dr == kMlaTcDr && !indices;
+}
 
 // Split count of the SIMT attention kernel: a function of the static shape only
 // (token capacity and CTA count), so that the host never reads a length.  148
@@ -96,6 +137,33 @@ int launch_attend_simt(const MlaParams& p, cudaStream_t stream) {
     if (rc != 0) return rc;
     if (p.splits > 1) {
         mla_merge_kernel<T><<<(unsigned)(rows * p.heads), 128, 0, stream>>>(p);
+        rc = (int)cudaGetLastError();
+    }
+    return rc;
+}
+
+template <typename T>
+int launch_attend_tc(const MlaParams& p, cudaStream_t stream) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    constexpr int slot = std::is_same<T, __half>::value ? 0 : 1;
+    if (!g_mla_tc_ready[dev][slot]) {
+        e = cudaFuncSetAttribute(mla_attend_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 MlaTcGeom::kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        g_mla_tc_ready[dev][slot] = true;
+    }
+    int* status = nullptr;
+    e = mla_tc_status_address(&status);
+    if (e != cudaSuccess) return (int)e;
+    const int R = p.tq * p.heads;
+    const dim3 grid((unsigned)(2 * p.splits), (unsigned)((R + kMlaTcRows - 1) / kMlaTcRows), (unsigned)p.batch);
+    mla_attend_tc_kernel<T><<<grid, kMlaTcThreads, MlaTcGeom::kSmemBytes, stream>>>(p, status);
+    int rc = (int)cudaGetLastError();
+    if (rc != 0) return rc;
+    if (p.splits > 1) {
+        mla_merge_kernel<T><<<(unsigned)((long long)p.batch * R), 128, 0, stream>>>(p);
         rc = (int)cudaGetLastError();
     }
     return rc;
@@ -170,8 +238,16 @@ size_t mla_b200_attend_workspace_bytes(int batch, int tq, int heads, int dc, int
     if (check_attend_shape(GQA_B200_F32, batch, tq, heads, dc, dr, 1, page, max_pages, nk) != 0) return 0;
     const long long rows = (long long)batch * tq;
     const int capacity = nk > 0 ? nk : page * max_pages;
-    const size_t simt = partial_bytes(rows, heads, dc, simt_auto_splits(rows, heads, capacity));
-    return simt > 256 ? simt : 256;
+    size_t need = partial_bytes(rows, heads, dc, simt_auto_splits(rows, heads, capacity));
+    if (dc == kMlaTcDc && dr == kMlaTcDr && nk == 0) {
+        int sms = 0, chunk = 0, splits = 1;
+        if (sm_count(&sms) != cudaSuccess) sms = 148;
+        const long long units = (long long)batch * (((long long)tq * heads + kMlaTcRows - 1) / kMlaTcRows);
+        tc_chunking(units, capacity, sms / 2, &chunk, &splits);
+        const size_t tc = partial_bytes(rows, heads, dc, splits);
+        if (tc > need) need = tc;
+    }
+    return need > 256 ? need : 256;
 }
 
 int mla_b200_attend_ex(const void* q_absorbed, const void* q_rope, const void* cache,
@@ -188,7 +264,14 @@ int mla_b200_attend_ex(const void* q_absorbed, const void* q_rope, const void* c
     if (!q_absorbed || !q_rope || !cache || !block_table || !lengths || !positions || !out)
         return GQA_B200_ERR_NULL_POINTER;
     if (indices && nk <= 0) return MLA_B200_ERR_SHAPE;
-    if (kernel != MLA_B200_KERNEL_AUTO && kernel != MLA_B200_KERNEL_SIMT) return GQA_B200_ERR_KERNEL;
+    if (kernel != MLA_B200_KERNEL_AUTO && kernel != MLA_B200_KERNEL_SIMT && kernel != MLA_B200_KERNEL_TCGEN05)
+        return GQA_B200_ERR_KERNEL;
+    auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+    const bool tc_ok = tc_eligible(dtype, dc, dr, indices) && aligned16(q_absorbed) && aligned16(q_rope) &&
+                       aligned16(cache) && aligned16(out) && (long long)tq * heads <= 65535LL * kMlaTcRows &&
+                       batch <= 65535;
+    if (kernel == MLA_B200_KERNEL_TCGEN05 && !tc_ok) return GQA_B200_ERR_KERNEL;
+    const bool use_tc = tc_ok && kernel != MLA_B200_KERNEL_SIMT;
 
     const long long rows = (long long)batch * tq;
     const int capacity = indices ? nk : page * max_pages;
@@ -199,7 +282,21 @@ int mla_b200_attend_ex(const void* q_absorbed, const void* q_rope, const void* c
     p.batch = batch; p.tq = tq; p.heads = heads; p.dc = dc; p.dr = dr; p.page = page;
     p.max_pages = max_pages; p.nk = indices ? nk : 0; p.causal = causal ? 1 : 0;
     p.scale_log2 = scale * kLog2e;
-    p.splits = splits > 0 ? splits : simt_auto_splits(rows, heads, capacity);
+    p.page_shift = (page & (page - 1)) == 0 ? __builtin_ctz((unsigned)page) : -1;
+    if (use_tc) {
+        int sms = 0;
+        cudaError_t e = sm_count(&sms);
+        if (e != cudaSuccess) return (int)e;
+        const long long units = (long long)batch * (((long long)tq * heads + kMlaTcRows - 1) / kMlaTcRows);
+        tc_chunking(units, capacity, sms / 2, &p.chunk_tokens, &p.splits);
+        if (splits > 0) {                            // explicit split count: equal chunks of the capacity
+            if (splits > 32767) return GQA_B200_ERR_SPLITS;
+            p.splits = splits;
+            p.chunk_tokens = ((capacity + splits - 1) / splits + kMlaTcBN - 1) / kMlaTcBN * kMlaTcBN;
+        }
+    } else {
+        p.splits = splits > 0 ? splits : simt_auto_splits(rows, heads, capacity);
+    }
     if (p.splits > 1) {
         const size_t need = partial_bytes(rows, heads, dc, p.splits);
         if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < need)
@@ -207,6 +304,10 @@ int mla_b200_attend_ex(const void* q_absorbed, const void* q_rope, const void* c
         const size_t n = (size_t)rows * heads * p.splits;
         p.part_ml = static_cast<float*>(workspace);
         p.part_acc = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(n * 2 * sizeof(float), 256));
+    }
+    if (use_tc) {
+        if (dtype == GQA_B200_F16) return launch_attend_tc<__half>(p, static_cast<cudaStream_t>(stream));
+        return launch_attend_tc<__nv_bfloat16>(p, static_cast<cudaStream_t>(stream));
     }
     return by_dtype(dtype, [&](auto tag) {
         return launch_attend_simt<decltype(tag)>(p, static_cast<cudaStream_t>(stream));
@@ -264,8 +365,18 @@ int mla_b200_decode(const void* q_nope, const void* q_rope, const void* cache,
 }
 
 int mla_b200_tc_status(int reset) {
-    (void)reset;
-    return 0;
+    int* status = nullptr;
+    cudaError_t e = mla_tc_status_address(&status);
+    if (e != cudaSuccess) return -(int)e;
+    int host = 0;
+    e = cudaMemcpy(&host, status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return -(int)e;
+    if (reset) {
+        const int zero = 0;
+        e = cudaMemcpy(status, &zero, sizeof(int), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) return -(int)e;
+    }
+    return host;
 }
 
 }  // extern "C"

@@ -20,6 +20,8 @@ struct MlaParams {
     float* part_acc;           // [rows * heads][splits][dc]  unnormalised
     long long num_blocks;
     int batch, tq, heads, dc, dr, page, max_pages, nk, splits, causal;
+    int chunk_tokens;          // tensor-core kernel: tokens per split (split s covers [s, s+1) * chunk_tokens)
+    int page_shift;            // log2(page) when page is a power of two, else -1
     float scale_log2;          // scale * log2(e)
 };
 

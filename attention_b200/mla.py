@@ -202,3 +202,9 @@ def mla_decode(q_nope, q_rope, cache, block_table, lengths, positions, w_uk, w_u
             stream)
     _raise_status(rc, "mla_decode")
     return out
+
+
+def mla_tc_status(reset: bool = False) -> int:
+    """Status word of the tensor-core attention kernel's bounded waits on the current device
+    (0 = no wait ever ran out).  Synchronises the device."""
+    return int(_lib().mla_b200_tc_status(1 if reset else 0))

@@ -184,3 +184,64 @@ def test_mla_deepseek_shape_small_batch():
                                            c["lengths"], c["positions"], c["w_uk"], c["w_uv"],
                                            round_intermediates=True)
     _close(got, want, torch.bfloat16)
+
+
+# ------------------------------------------------------------- tensor-core kernel (CTA pair)
+def _tc_case(heads, tq, page, lengths, dtype=torch.bfloat16, seed=5):
+    w = synth.MlaWorkload("t", len(lengths), tq, heads, 32, 64, 512, 32, page, dtype, 0, 0)
+    return w, synth.make_mla_case(w, lengths=lengths, seed=seed)
+
+
+def _latent(c, d, kernel, splits=0, causal=True):
+    scale = 0.06
+    qa = attn.mla_query_absorb(d["q_nope"], d["w_uk"])
+    got = attn.mla_latent_attention(qa, d["q_rope"], d["cache"], d["block_table"], d["lengths"],
+                                    d["positions"], scale=scale, causal=causal, kernel=kernel, splits=splits)
+    want = mla_oracle.reference_mla_latent_attention(qa.cpu(), c["q_rope"], c["cache"], c["block_table"],
+                                                     c["lengths"], c["positions"], scale=scale, causal=causal)
+    return got, want
+
+
+@gpu
+@pytest.mark.parametrize("heads,tq,page,lengths,dtype", [
+    (128, 1, 64, [700, 64, 1, 0, 33], torch.bfloat16),
+    (16, 1, 64, [300, 31, 32, 257], torch.bfloat16),
+    (128, 2, 16, [130, 5], torch.float16),            # two row tiles per sequence
+    (24, 3, 48, [100, 49, 200], torch.bfloat16),      # rows of several query tokens share a tile; odd page size
+    (5, 1, 8, [1000], torch.float16),
+])
+def test_mla_tensor_core_kernel_matches_oracle(heads, tq, page, lengths, dtype):
+    from attention_b200.mla import mla_tc_status
+    mla_tc_status(reset=True)
+    w, c = _tc_case(heads, tq, page, lengths, dtype)
+    d = _dev(c)
+    for splits in (0, 1, 3):
+        got, want = _latent(c, d, "tcgen05", splits=splits)
+        _close(got, want, dtype)
+    simt, _ = _latent(c, d, "simt")
+    _close(got, simt, dtype)
+    assert mla_tc_status() == 0
+
+
+@gpu
+def test_mla_tensor_core_kernel_non_causal_and_early_positions():
+    from attention_b200.mla import mla_tc_status
+    w, c = _tc_case(32, 2, 32, [90, 40])
+    c["positions"] = torch.tensor([[10, 80], [-1, 39]], dtype=torch.int32)
+    d = _dev(c)
+    got, want = _latent(c, d, "tcgen05")
+    _close(got, want, torch.bfloat16)
+    assert torch.count_nonzero(got[1, 0]) == 0
+    got, want = _latent(c, d, "tcgen05", causal=False)
+    _close(got, want, torch.bfloat16)
+    assert mla_tc_status() == 0
+
+
+@gpu
+def test_mla_tensor_core_kernel_refuses_other_shapes():
+    w = synth.MLA_WORKLOADS["m1_small_fp32"]
+    d = _dev(synth.make_mla_case(w))
+    qa = attn.mla_query_absorb(d["q_nope"], d["w_uk"])
+    with pytest.raises(RuntimeError, match="kernel"):
+        attn.mla_latent_attention(qa, d["q_rope"], d["cache"], d["block_table"], d["lengths"], d["positions"],
+                                  scale=0.1, kernel="tcgen05")
