@@ -15,19 +15,25 @@
 // distributed shared memory and adds what it receives, so both CTAs hold the same scores bit
 // for bit (a + b == b + a) and take the same softmax decisions without further talk.
 //
-// Per CTA: Q_r (80 KB), a five-stage ring of 32-token tiles (20 KB each, 16-byte cp.async
-// with the page lookup per row), the P tile, and the 16 KB landing buffer for the peer's
-// partial scores: 212 KB, one CTA per SM.  TMEM: three score buffers of 32 columns and 256
-// columns of output.  Tiles are loaded four ahead, Q.C^T is issued two tiles ahead of the
-// softmax, P.C is issued as soon as P is in shared memory.
+// Per CTA: Q_r (80 KB), a five-stage ring of 32-token tiles (20 KB each), the P tile, and the
+// 16 KB landing buffer for the peer's partial scores: 212 KB, one CTA per SM.  TMEM: three score
+// buffers of 32 columns and 256 columns of output.
 //
-// Hand-offs (mbarriers; every wait is time-bounded, a wait that runs out marks the CTA dead,
-// raises the status word, and the CTA still walks the protocol to the end so that its peer is
-// never left waiting and no CTA exits while the other may still write into its memory):
-//   bar_s[3]   tcgen05.commit   partial scores of a tile are in TMEM
-//   bar_pv     tcgen05.commit   P.C of a tile is done: its stage, the P tile and O are free
-//   bar_x      256 remote arrivals   the peer's partial scores of a tile have landed here
-//   bar_free   256 remote arrivals   the peer has consumed what this CTA sent it
+// Warp roles (416 threads):
+//   warps 0-7    softmax: two threads per query row (16 score columns each)
+//   warps 8-11   loaders: 16-byte cp.async of this CTA's blocks of each cache row, one page lookup
+//                per tile when the page size is a multiple of 32 tokens, else one per row
+//   warp 12      one lane issues every tcgen05.mma
+// There is no CTA-wide barrier in the token loop; the hand-offs are mbarriers.  Every wait is
+// time-bounded: a wait that runs out marks the CTA dead and raises the status word, and the CTA
+// still walks the protocol to the end, so its peer is never left waiting and no CTA exits
+// while the other may still write into its memory.
+//   full[5]    128 loader arrivals (when their copies land)  tile is in its stage   -> MMA lane
+//   empty[5]   tcgen05.commit   P.C of the stage's tile is done: stage, P tile, O are free
+//   bar_s[3]   tcgen05.commit   partial scores of a tile are in TMEM                -> softmax
+//   bar_p      8 warp arrivals  P is in shared memory, scores read, O rescaled      -> MMA lane
+//   bar_x      transaction barrier: the peer's st.async stores complete its 16 KB per tile
+//   bar_free   8 remote warp arrivals   the peer has consumed what this CTA sent it
 #pragma once
 
 #include <type_traits>
@@ -41,9 +47,10 @@ namespace gqa_b200 {
 
 constexpr int kMlaTcRows = 128;        // query rows (token x head) per CTA pair
 constexpr int kMlaTcBN = 32;           // tokens per tile
-constexpr int kMlaTcThreads = 256;
+constexpr int kMlaTcSoftmaxThreads = 256;
+constexpr int kMlaTcLoadThreads = 128;
+constexpr int kMlaTcThreads = kMlaTcSoftmaxThreads + kMlaTcLoadThreads + 32;
 constexpr int kMlaTcStages = 5;
-constexpr int kMlaTcAhead = 4;         // tiles loaded ahead of the softmax
 constexpr int kMlaTcSBufs = 3;
 constexpr int kMlaTcTmemCols = 512;
 constexpr int kMlaTcDc = 512;
@@ -82,9 +89,26 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared::cluster.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d)
-                 : "memory");
+// 16-byte store into another CTA's shared memory that, when it lands, completes 16 bytes of the
+// transaction count of an mbarrier in that CTA: data and signal travel together, no fence.
+__device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d,
+                                            uint32_t cluster_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1,%2,%3,%4}, [%5];"
+                 ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(cluster_bar) : "memory");
+}
+// the single arrival of a phase of a transaction barrier, announcing the bytes that will land
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote_relaxed(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// the barrier receives this thread's arrival once all of its earlier cp.async copies have landed
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 // mbar_wait with cluster-scope acquire: orders the peer CTA's stores before the reads that follow.
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, uint64_t max_ns) {
@@ -113,19 +137,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMlaTcThreads, 1)
 mla_attend_tc_kernel(const MlaParams p, int* status) {
     using G = MlaTcGeom;
     using Ops = MmaOps<T>;
-    constexpr int BM = kMlaTcRows, BN = kMlaTcBN, NT = kMlaTcThreads;
-    constexpr int NS = kMlaTcStages, LA = kMlaTcAhead, NSB = kMlaTcSBufs;
+    constexpr int BM = kMlaTcRows, BN = kMlaTcBN, NT = kMlaTcSoftmaxThreads, NL = kMlaTcLoadThreads;
+    constexpr int NS = kMlaTcStages, NSB = kMlaTcSBufs;
     constexpr int AB_TYPE = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-    constexpr int HC = BN / 2;                       // score columns per thread
+    constexpr int HC = BN / 2;                       // score columns per softmax thread
 
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ __align__(8) uint64_t s_bar[NSB + 3]; // S ready x3, P.C done, peer scores landed, peer consumed
+    __shared__ __align__(8) uint64_t s_bar[2 * NS + NSB + 3];
     __shared__ uint32_t s_tmem;
     __shared__ int s_dead;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int quad = warp & 3, hf = warp >> 2;       // TMEM lane quadrant, column half
-    const int row_l = quad * 32 + lane;              // this thread's row of the 128-row tile
+    const bool is_softmax = tid < NT, is_loader = tid >= NT && tid < NT + NL, is_mma = tid >= NT + NL;
+    const int quad = warp & 3, hf = (warp >> 2) & 1; // softmax warps: TMEM lane quadrant, column half
+    const int row_l = quad * 32 + lane;              // softmax thread's row of the 128-row tile
     const uint32_t rank = tc::cluster_ctarank(), peer = rank ^ 1u;
     const int chunk = blockIdx.x >> 1, b = blockIdx.z;
     const int R = p.tq * p.heads;                    // query rows of one sequence
@@ -135,15 +160,14 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
 
     int end_max = 0;
     for (int t = g0 / p.heads; t <= (min(R, g0 + BM) - 1) / p.heads; ++t) end_max = max(end_max, mla_row_end(p, b, t));
-    const int my_end = g < R ? mla_row_end(p, b, g / p.heads) : 0;
     const int t0 = chunk * p.chunk_tokens;
     const int t1 = min(end_max, t0 + p.chunk_tokens);
     const int n_tiles = t1 > t0 ? (t1 - t0 + BN - 1) / BN : 0;
-    const long long grow = (long long)b * R + g;     // global query row
+    const long long grow = (long long)b * R + g;     // global query row (softmax threads)
     T* op = reinterpret_cast<T*>(p.out);
 
     if (n_tiles == 0) {                              // nothing visible in this chunk (both CTAs agree)
-        if (g < R) {
+        if (is_softmax && g < R) {
             if (p.splits > 1) {
                 if (rank == 0 && hf == 0) {
                     p.part_ml[(grow * p.splits + chunk) * 2] = -INFINITY;
@@ -164,74 +188,32 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         return;
     }
     const uint32_t sq = s_base, sk = s_base + G::kOffK, sp = s_base + G::kOffP, sx = s_base + G::kOffX;
-    const uint32_t bar_s0 = tc::smem_u32(&s_bar[0]);
-    const uint32_t bar_pv = tc::smem_u32(&s_bar[NSB]);
-    const uint32_t bar_x = tc::smem_u32(&s_bar[NSB + 1]);
-    const uint32_t bar_free = tc::smem_u32(&s_bar[NSB + 2]);
-    const uint32_t peer_sx = tc::map_to_cta(sx, peer);
-    const uint32_t peer_bar_x = tc::map_to_cta(bar_x, peer);
-    const uint32_t peer_bar_free = tc::map_to_cta(bar_free, peer);
+    const uint32_t bar_full = tc::smem_u32(&s_bar[0]);
+    const uint32_t bar_empty = tc::smem_u32(&s_bar[NS]);
+    const uint32_t bar_s0 = tc::smem_u32(&s_bar[2 * NS]);
+    const uint32_t bar_p = tc::smem_u32(&s_bar[2 * NS + NSB]);
+    const uint32_t bar_x = tc::smem_u32(&s_bar[2 * NS + NSB + 1]);
+    const uint32_t bar_free = tc::smem_u32(&s_bar[2 * NS + NSB + 2]);
 
     if (warp == 0) { tc::tmem_alloc(tc::smem_u32(&s_tmem), kMlaTcTmemCols); tc::tmem_relinquish(); }
     if (tid == 0) {
 #pragma unroll
+        for (int i = 0; i < NS; ++i) { tc::mbar_init(bar_full + i * 8, NL); tc::mbar_init(bar_empty + i * 8, 1); }
+#pragma unroll
         for (int i = 0; i < NSB; ++i) tc::mbar_init(bar_s0 + i * 8, 1);
-        tc::mbar_init(bar_pv, 1);
-        tc::mbar_init(bar_x, NT);
-        tc::mbar_init(bar_free, NT);
+        tc::mbar_init(bar_p, NT / 32);               // one arrival per softmax warp
+        tc::mbar_init(bar_x, 1);                     // one local arrival announcing the bytes per tile
+        tc::mbar_init(bar_free, NT / 32);            // one arrival per peer softmax warp
         tc::fence_mbar_init();
+        tc::mbar_arrive_expect_tx(bar_x, G::kXBytes);   // tile 0
         s_dead = 0;
     }
-
-    // ---- asynchronous copies into swizzled tiles: [64-column block][row][128 B] ----
-    const int cpr = nb * 8;                          // 16-byte chunks of a row that this CTA owns
-    {
-        const T* qa = reinterpret_cast<const T*>(p.q);
-        const T* qr = reinterpret_cast<const T*>(p.qr);
-        for (int i = tid; i < BM * cpr; i += NT) {
-            const int row = i / cpr, c = i - row * cpr;
-            const bool valid = g0 + row < R;
-            const long long gr = (long long)b * R + (valid ? g0 + row : 0);
-            const int col = col0 + c * 8;
-            const T* src = col < kMlaTcDc ? qa + gr * kMlaTcDc + col : qr + gr * kMlaTcDr + (col - kMlaTcDc);
-            cp_async16<0>(sq + (c >> 3) * G::kQBlockBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4), src,
-                          valid ? 16 : 0, 0);
-        }
-    }
-    const char* cache = reinterpret_cast<const char*>(p.cache);
-    const int32_t* trow = p.table + (long long)b * p.max_pages;
-    const int last_block = (int)(p.num_blocks - 1);
-    auto load_tile = [&](int j) {                    // tile j of this chunk into stage j % NS
-        const uint32_t st = sk + (j % NS) * G::kStageBytes;
-        for (int i = tid; i < BN * cpr; i += NT) {
-            const int row = i / cpr, c = i - row * cpr;
-            const int tok = t0 + j * BN + row;
-            const bool valid = tok < t1;
-            const char* src = cache;
-            if (valid) {
-                const int pg = p.page_shift >= 0 ? tok >> p.page_shift : tok / p.page;
-                const int slot = tok - pg * p.page;
-                // a page id outside the pool (a caller error) is clamped instead of faulting
-                const long long phys = min(max(__ldg(trow + pg), 0), last_block);
-                src = cache + ((phys * p.page + slot) * kMlaTcWidth + col0 + c * 8) * 2;
-            }
-            cp_async16<0>(st + (c >> 3) * G::kTileBlockBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4), src,
-                          valid ? 16 : 0, 0);
-        }
-    };
-    load_tile(0);                                    // rides in the same group as Q
-    cp_async_commit();
-#pragma unroll
-    for (int j = 1; j < LA; ++j) {
-        if (j < n_tiles) load_tile(j);
-        cp_async_commit();
-    }
-
-    const int my_stop = min(my_end, t1);             // this row sees tokens [t0, my_stop) of the chunk
-    float m_run = -INFINITY, l_run = 0.f;
-    const uint32_t idesc_s = tc::idesc_f16(BM, BN, AB_TYPE);
-    const uint32_t idesc_o = tc::idesc_f16(BM, 256, AB_TYPE) | tc::kIdescBMnMajor;
-    const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::cluster_sync_all();                          // both CTAs' barriers exist before any remote arrival
+    tc::tc_fence_after();
+    const uint32_t tmem = s_tmem;
+    const uint32_t tmem_o = tmem + NSB * BN;
     bool alive = true;
 
     auto timed_out = [&]() {
@@ -246,186 +228,271 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         if (!tc::mbar_wait_cluster(bar, parity, s_dead ? 1000ull : 1000000000ull)) timed_out();
     };
 
-    cp_async_wait<1>();                              // Q and tiles 0 .. LA-2 have landed
-    tc::fence_async_smem();
-    tc::tc_fence_before();
-    __syncthreads();
-    tc::cluster_sync_all();                          // both CTAs' barriers exist before any remote arrival
-    tc::tc_fence_after();
-    const uint32_t tmem = s_tmem;
-    const uint32_t tmem_o = tmem + NSB * BN;
-
-    // S_r(j) = Q_r C_r(j)^T into score buffer j % NSB (one thread)
-    auto issue_qk = [&](int j) {
-        const uint32_t st = sk + (j % NS) * G::kStageBytes;
-        const uint32_t d = tmem + (j % NSB) * BN;
-        for (int blk = 0; blk < nb; ++blk) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const uint64_t da = tc::smem_desc_sw128_kmajor(sq + blk * G::kQBlockBytes + k * 32);
-                const uint64_t db = tc::smem_desc_sw128_kmajor(st + blk * G::kTileBlockBytes + k * 32);
-                tc::mma_f16_ss(d, da, db, idesc_s, (blk | k) ? 1u : 0u);
+    if (is_loader) {
+        // =============================== loader warps ===============================
+        const int lt = tid - NT;
+        const int cpr = nb * 8;                      // 16-byte chunks of a row that this CTA owns
+        {   // Q_r: [block][128 rows][128 B], rides with tile 0 on full[0]
+            const T* qa = reinterpret_cast<const T*>(p.q);
+            const T* qr = reinterpret_cast<const T*>(p.qr);
+            for (int i = lt; i < BM * cpr; i += NL) {
+                const int row = i / cpr, c = i - row * cpr;
+                const bool valid = g0 + row < R;
+                const long long gr = (long long)b * R + (valid ? g0 + row : 0);
+                const int col = col0 + c * 8;
+                const T* src = col < kMlaTcDc ? qa + gr * kMlaTcDc + col : qr + gr * kMlaTcDr + (col - kMlaTcDc);
+                cp_async16<0>(sq + (c >> 3) * G::kQBlockBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4), src,
+                              valid ? 16 : 0, 0);
             }
         }
-        tc::mma_commit(bar_s0 + (j % NSB) * 8);
-    };
-    // O_r += P C_r(j): the first four blocks of the stage, as an MN-major operand (one thread)
-    auto issue_pv = [&](int j) {
-        const uint32_t st = sk + (j % NS) * G::kStageBytes;
+        // this thread's chunks of a tile: the same (row, 16-byte column) for every tile
+        constexpr int MAXC = BN * 40 / NL;           // 10 chunks per thread for rank 1, 8 for rank 0
+        const int nchunk = BN * cpr / NL;
+        uint32_t soff[MAXC], doff[MAXC];             // byte offsets in the cache page run / in the stage
 #pragma unroll
-        for (int k = 0; k < BN / 16; ++k) {
-            const uint64_t da = tc::smem_desc_sw128_kmajor(sp + k * 32);
-            const uint64_t db = tc::smem_desc_sw128_mnmajor(st + k * 2048, G::kTileBlockBytes);
-            tc::mma_f16_ss(tmem_o, da, db, idesc_o, (j | k) ? 1u : 0u);
+        for (int k = 0; k < MAXC; ++k) {
+            const int i = lt + k * NL;
+            const int row = i / cpr, c = i - row * cpr;
+            soff[k] = (uint32_t)(row * kMlaTcWidth + col0 + c * 8) * 2u;
+            doff[k] = (uint32_t)((c >> 3) * G::kTileBlockBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4));
         }
-        tc::mma_commit(bar_pv);
-    };
-
-    if (tid == 0) {
-        issue_qk(0);
-        if (n_tiles > 1) issue_qk(1);
-    }
-
-    for (int j = 0; j < n_tiles; ++j) {
-        // ---- this CTA's partial scores of tile j ----
-        wait_bar(bar_s0 + (j % NSB) * 8, (j / NSB) & 1);
-        tc::tc_fence_after();
-        uint32_t r[32];
-        tc::tmem_ld32(tmem + (j % NSB) * BN + lane_sel, r);
-        tc::tmem_ld_wait();
-        // ---- send this thread's 16 columns to the peer (once it has consumed the previous tile) ----
-        if (j > 0) wait_bar_cluster(bar_free, (j - 1) & 1);
+        const char* cache = reinterpret_cast<const char*>(p.cache);
+        const int32_t* trow = p.table + (long long)b * p.max_pages;
+        const int last_block = (int)(p.num_blocks - 1);
+        const bool page_run = p.page_shift >= 5;     // a 32-token tile never straddles a page
+        for (int j = 0; j < n_tiles; ++j) {
+            const int stage = j % NS;
+            if (j >= NS) wait_bar(bar_empty + stage * 8, ((j / NS) - 1) & 1);
+            const uint32_t st = sk + stage * G::kStageBytes;
+            const int tok0 = t0 + j * BN;
+            if (page_run) {
+                const int pg = tok0 >> p.page_shift;
+                // a page id outside the pool (a caller error) is clamped instead of faulting
+                const long long phys = min(max(__ldg(trow + pg), 0), last_block);
+                const char* base = cache + (phys * p.page + (tok0 & (p.page - 1))) * (kMlaTcWidth * 2);
+                const int rows_ok = t1 - tok0;       // rows below this are inside the chunk
 #pragma unroll
-        for (int q4 = 0; q4 < HC / 4; ++q4) {        // (register arrays are indexed statically: select by hf)
-            const int lo = q4 * 4, hi = HC + q4 * 4;
-            tc::st_cluster_v4(peer_sx + ((hf * (HC / 4) + q4) * BM + row_l) * 16, hf ? r[hi] : r[lo],
-                              hf ? r[hi + 1] : r[lo + 1], hf ? r[hi + 2] : r[lo + 2], hf ? r[hi + 3] : r[lo + 3]);
-        }
-        tc::mbar_arrive_remote(peer_bar_x);
-        // tile j+2 landed before the barrier that ended iteration j-1; its score buffer was read in j-1
-        if (tid == 0 && j + 2 < n_tiles) issue_qk(j + 2);
-
-        // ---- full scores = mine + the peer's ----
-        wait_bar_cluster(bar_x, j & 1);
-        float s[BN];
-#pragma unroll
-        for (int c4 = 0; c4 < BN / 4; ++c4) {
-            uint32_t x0, x1, x2, x3;
-            asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3)
-                         : "r"(sx + (c4 * BM + row_l) * 16) : "memory");
-            s[c4 * 4 + 0] = __uint_as_float(r[c4 * 4 + 0]) + __uint_as_float(x0);
-            s[c4 * 4 + 1] = __uint_as_float(r[c4 * 4 + 1]) + __uint_as_float(x1);
-            s[c4 * 4 + 2] = __uint_as_float(r[c4 * 4 + 2]) + __uint_as_float(x2);
-            s[c4 * 4 + 3] = __uint_as_float(r[c4 * 4 + 3]) + __uint_as_float(x3);
-        }
-        tc::mbar_arrive_remote(peer_bar_free);       // the peer may overwrite the landing buffer
-        const int tok0 = t0 + j * BN;
-        if (tok0 + BN > my_stop) {
-#pragma unroll
-            for (int c = 0; c < BN; ++c)
-                if (tok0 + c >= my_stop) s[c] = -INFINITY;
-        }
-        float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < BN; c += 4) {
-            a0 = fmaxf(a0, s[c]); a1 = fmaxf(a1, s[c + 1]); a2 = fmaxf(a2, s[c + 2]); a3 = fmaxf(a3, s[c + 3]);
-        }
-        const float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * p.scale_log2;
-        const bool need = mx > m_run + kRescaleSlack;
-        float alpha = 1.f;
-        if (need) {
-            const float mn = fmaxf(m_run, mx);
-            alpha = m_run == -INFINITY ? 0.f : fast_exp2(m_run - mn);
-            m_run = mn;
-            l_run *= alpha;
-        }
-        const float ref = m_run == -INFINITY ? 0.f : m_run;
-        uint32_t pw[HC / 2];
-        {
-            float ps0 = 0.f, ps1 = 0.f;
-#pragma unroll
-            for (int c = 0; c < HC; c += 2) {
-                const float p0 = fast_exp2(fmaf(hf ? s[HC + c] : s[c], p.scale_log2, -ref));
-                const float p1 = fast_exp2(fmaf(hf ? s[HC + c + 1] : s[c + 1], p.scale_log2, -ref));
-                ps0 += p0; ps1 += p1;
-                pw[c / 2] = Ops::pack(p0, p1);
-            }
-            l_run += ps0 + ps1;                      // this thread's half of the row sum
-        }
-
-        // ---- P.C(j-1) is done: its stage, the P tile and O may be touched ----
-        if (j > 0) wait_bar(bar_pv, (j - 1) & 1);
-        tc::tc_fence_after();
-        if (j + LA < n_tiles) load_tile(j + LA);     // into the stage tile j-1 used
-        cp_async_commit();
-        if (j > 0 && __any_sync(0xffffffffu, need)) {   // warp-uniform: TMEM ld/st are collective
-#pragma unroll
-            for (int c0 = hf * 128; c0 < (hf + 1) * 128; c0 += 32) {
-                uint32_t o[32];
-                tc::tmem_ld32(tmem_o + lane_sel + c0, o);
-                tc::tmem_ld_wait();
-#pragma unroll
-                for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-                tc::tmem_st32(tmem_o + lane_sel + c0, o);
-            }
-            tc::tmem_st_wait();
-        }
-#pragma unroll
-        for (int c8 = 0; c8 < HC / 8; ++c8) {
-            const int ch = hf * (HC / 8) + c8;
-            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(sp + row_l * 128 + ((ch ^ (row_l & 7)) << 4)),
-                         "r"(pw[c8 * 4 + 0]), "r"(pw[c8 * 4 + 1]), "r"(pw[c8 * 4 + 2]), "r"(pw[c8 * 4 + 3])
-                         : "memory");
-        }
-        cp_async_wait<1>();                          // tiles up to j + LA - 1 have landed (this thread's part)
-        tc::fence_async_smem();
-        tc::tc_fence_before();
-        __syncthreads();
-        if (tid == NT / 2) {
-            tc::tc_fence_after();
-            issue_pv(j);
-        }
-    }
-    wait_bar(bar_pv, (n_tiles - 1) & 1);
-    tc::tc_fence_after();
-
-    // ---- row sum = the two halves (exchanged through the idle P tile); store ----
-    float* s_half = reinterpret_cast<float*>(smem + G::kOffP);          // [2][128]
-    s_half[hf * BM + row_l] = l_run;
-    __syncthreads();
-    const float l_tot = l_run + s_half[(hf ^ 1) * BM + row_l];
-    const bool final_out = p.splits == 1;
-    const float inv = final_out ? (l_tot > 0.f ? 1.f / l_tot : 0.f) : 1.f;
-    float* pacc = final_out ? nullptr : p.part_acc + (grow * p.splits + chunk) * kMlaTcDc + col0;
-#pragma unroll
-    for (int c0 = hf * 128; c0 < (hf + 1) * 128; c0 += 32) {
-        uint32_t o[32];
-        tc::tmem_ld32(tmem_o + lane_sel + c0, o);
-        tc::tmem_ld_wait();
-        if (g < R && alive) {
-            if (final_out) {
-                uint4* dst = reinterpret_cast<uint4*>(op + grow * kMlaTcDc + col0 + c0);
-#pragma unroll
-                for (int c8 = 0; c8 < 4; ++c8) {
-                    uint4 v;
-                    v.x = Ops::pack(__uint_as_float(o[c8 * 8 + 0]) * inv, __uint_as_float(o[c8 * 8 + 1]) * inv);
-                    v.y = Ops::pack(__uint_as_float(o[c8 * 8 + 2]) * inv, __uint_as_float(o[c8 * 8 + 3]) * inv);
-                    v.z = Ops::pack(__uint_as_float(o[c8 * 8 + 4]) * inv, __uint_as_float(o[c8 * 8 + 5]) * inv);
-                    v.w = Ops::pack(__uint_as_float(o[c8 * 8 + 6]) * inv, __uint_as_float(o[c8 * 8 + 7]) * inv);
-                    dst[c8] = v;
+                for (int k = 0; k < MAXC; ++k) {
+                    if (k < nchunk) {
+                        const bool valid = (int)((doff[k] >> 7) & 31u) < rows_ok;
+                        cp_async16<0>(st + doff[k], valid ? base + soff[k] : cache, valid ? 16 : 0, 0);
+                    }
                 }
             } else {
-                uint4* dst = reinterpret_cast<uint4*>(pacc + c0);
 #pragma unroll
-                for (int c4 = 0; c4 < 8; ++c4) dst[c4] = make_uint4(o[c4 * 4], o[c4 * 4 + 1], o[c4 * 4 + 2], o[c4 * 4 + 3]);
+                for (int k = 0; k < MAXC; ++k) {
+                    if (k < nchunk) {
+                        const int row = (int)((doff[k] >> 7) & 31u);
+                        const int tok = tok0 + row;
+                        const bool valid = tok < t1;
+                        const char* src = cache;
+                        if (valid) {
+                            const int pg = p.page_shift >= 0 ? tok >> p.page_shift : tok / p.page;
+                            const long long phys = min(max(__ldg(trow + pg), 0), last_block);
+                            src = cache + (phys * p.page + (tok - pg * p.page)) * (kMlaTcWidth * 2) +
+                                  (soff[k] - (uint32_t)row * (kMlaTcWidth * 2));
+                        }
+                        cp_async16<0>(st + doff[k], src, valid ? 16 : 0, 0);
+                    }
+                }
+            }
+            tc::cp_async_arrive(bar_full + stage * 8);
+        }
+        cp_async_wait<0>();
+    } else if (is_mma) {
+        // =============================== MMA warp: one lane issues everything ===============================
+        if (lane == 0) {
+            const uint32_t idesc_s = tc::idesc_f16(BM, BN, AB_TYPE);
+            const uint32_t idesc_o = tc::idesc_f16(BM, 256, AB_TYPE) | tc::kIdescBMnMajor;
+            // S_r(j) = Q_r C_r(j)^T into score buffer j % NSB
+            auto issue_qk = [&](int j) {
+                const uint32_t st = sk + (j % NS) * G::kStageBytes;
+                const uint32_t d = tmem + (j % NSB) * BN;
+                for (int blk = 0; blk < nb; ++blk) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint64_t da = tc::smem_desc_sw128_kmajor(sq + blk * G::kQBlockBytes + k * 32);
+                        const uint64_t db = tc::smem_desc_sw128_kmajor(st + blk * G::kTileBlockBytes + k * 32);
+                        tc::mma_f16_ss(d, da, db, idesc_s, (blk | k) ? 1u : 0u);
+                    }
+                }
+                tc::mma_commit(bar_s0 + (j % NSB) * 8);
+            };
+            // O_r += P C_r(j): the first four blocks of the stage, as an MN-major operand
+            auto issue_pv = [&](int j) {
+                const uint32_t st = sk + (j % NS) * G::kStageBytes;
+#pragma unroll
+                for (int k = 0; k < BN / 16; ++k) {
+                    const uint64_t da = tc::smem_desc_sw128_kmajor(sp + k * 32);
+                    const uint64_t db = tc::smem_desc_sw128_mnmajor(st + k * 2048, G::kTileBlockBytes);
+                    tc::mma_f16_ss(tmem_o, da, db, idesc_o, (j | k) ? 1u : 0u);
+                }
+                tc::mma_commit(bar_empty + (j % NS) * 8);
+            };
+            wait_bar(bar_full, 0);                   // Q and tile 0
+            tc::fence_async_smem();
+            tc::tc_fence_after();
+            issue_qk(0);
+            for (int j = 0; j < n_tiles; ++j) {
+                if (j + 1 < n_tiles) {               // scores one tile ahead; buffer (j+1)%3 was read in j-2
+                    wait_bar(bar_full + ((j + 1) % NS) * 8, ((j + 1) / NS) & 1);
+                    tc::fence_async_smem();
+                    tc::tc_fence_after();
+                    issue_qk(j + 1);
+                }
+                wait_bar(bar_p, j & 1);              // P(j) stored, S(j) read, O rescaled
+                tc::tc_fence_after();
+                issue_pv(j);
             }
         }
+        __syncwarp();
+    } else {
+        // =============================== softmax warps ===============================
+        const uint32_t peer_sx = tc::map_to_cta(sx, peer);
+        const uint32_t peer_bar_x = tc::map_to_cta(bar_x, peer);
+        const uint32_t peer_bar_free = tc::map_to_cta(bar_free, peer);
+        const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+        const int my_end = g < R ? mla_row_end(p, b, g / p.heads) : 0;
+        const int my_stop = min(my_end, t1);         // this row sees tokens [t0, my_stop) of the chunk
+        float m_run = -INFINITY, l_run = 0.f;
+
+        for (int j = 0; j < n_tiles; ++j) {
+            // ---- this CTA's partial scores of tile j ----
+            wait_bar(bar_s0 + (j % NSB) * 8, (j / NSB) & 1);
+            tc::tc_fence_after();
+            uint32_t r[32];
+            tc::tmem_ld32(tmem + (j % NSB) * BN + lane_sel, r);
+            tc::tmem_ld_wait();
+            // ---- send this thread's 16 columns to the peer (once it has consumed the previous tile) ----
+            if (j > 0) wait_bar_cluster(bar_free, (j - 1) & 1);
+#pragma unroll
+            for (int q4 = 0; q4 < HC / 4; ++q4) {    // (register arrays are indexed statically: select by hf)
+                const int lo = q4 * 4, hi = HC + q4 * 4;
+                tc::st_async_v4(peer_sx + ((hf * (HC / 4) + q4) * BM + row_l) * 16, hf ? r[hi] : r[lo],
+                                hf ? r[hi + 1] : r[lo + 1], hf ? r[hi + 2] : r[lo + 2], hf ? r[hi + 3] : r[lo + 3],
+                                peer_bar_x);
+            }
+
+            // ---- full scores = mine + the peer's ----
+            wait_bar(bar_x, j & 1);
+            // announce the next tile's bytes; they cannot land before every warp here has passed the
+            // wait above, because the peer sends only after all warps have released the buffer below
+            if (tid == 0 && j + 1 < n_tiles) tc::mbar_arrive_expect_tx(bar_x, G::kXBytes);
+            float s[BN];
+#pragma unroll
+            for (int c4 = 0; c4 < BN / 4; ++c4) {
+                uint32_t x0, x1, x2, x3;
+                asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3)
+                             : "r"(sx + (c4 * BM + row_l) * 16) : "memory");
+                s[c4 * 4 + 0] = __uint_as_float(r[c4 * 4 + 0]) + __uint_as_float(x0);
+                s[c4 * 4 + 1] = __uint_as_float(r[c4 * 4 + 1]) + __uint_as_float(x1);
+                s[c4 * 4 + 2] = __uint_as_float(r[c4 * 4 + 2]) + __uint_as_float(x2);
+                s[c4 * 4 + 3] = __uint_as_float(r[c4 * 4 + 3]) + __uint_as_float(x3);
+            }
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive_remote_relaxed(peer_bar_free);   // the peer may overwrite the buffer
+            const int tok0 = t0 + j * BN;
+            if (tok0 + BN > my_stop) {
+#pragma unroll
+                for (int c = 0; c < BN; ++c)
+                    if (tok0 + c >= my_stop) s[c] = -INFINITY;
+            }
+            float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < BN; c += 4) {
+                a0 = fmaxf(a0, s[c]); a1 = fmaxf(a1, s[c + 1]); a2 = fmaxf(a2, s[c + 2]); a3 = fmaxf(a3, s[c + 3]);
+            }
+            const float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * p.scale_log2;
+            const bool need = mx > m_run + kRescaleSlack;
+            float alpha = 1.f;
+            if (need) {
+                const float mn = fmaxf(m_run, mx);
+                alpha = m_run == -INFINITY ? 0.f : fast_exp2(m_run - mn);
+                m_run = mn;
+                l_run *= alpha;
+            }
+            const float ref = m_run == -INFINITY ? 0.f : m_run;
+            uint32_t pw[HC / 2];
+            {
+                float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+                for (int c = 0; c < HC; c += 2) {
+                    const float p0 = fast_exp2(fmaf(hf ? s[HC + c] : s[c], p.scale_log2, -ref));
+                    const float p1 = fast_exp2(fmaf(hf ? s[HC + c + 1] : s[c + 1], p.scale_log2, -ref));
+                    ps0 += p0; ps1 += p1;
+                    pw[c / 2] = Ops::pack(p0, p1);
+                }
+                l_run += ps0 + ps1;                  // this thread's half of the row sum
+            }
+
+            // ---- P.C(j-1) is done: the P tile and O may be touched ----
+            if (j > 0) wait_bar(bar_empty + ((j - 1) % NS) * 8, ((j - 1) / NS) & 1);
+            tc::tc_fence_after();
+            if (j > 0 && __any_sync(0xffffffffu, need)) {   // warp-uniform: TMEM ld/st are collective
+#pragma unroll
+                for (int c0 = hf * 128; c0 < (hf + 1) * 128; c0 += 32) {
+                    uint32_t o[32];
+                    tc::tmem_ld32(tmem_o + lane_sel + c0, o);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+                    tc::tmem_st32(tmem_o + lane_sel + c0, o);
+                }
+                tc::tmem_st_wait();
+            }
+#pragma unroll
+            for (int c8 = 0; c8 < HC / 8; ++c8) {
+                const int ch = hf * (HC / 8) + c8;
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(sp + row_l * 128 + ((ch ^ (row_l & 7)) << 4)),
+                             "r"(pw[c8 * 4 + 0]), "r"(pw[c8 * 4 + 1]), "r"(pw[c8 * 4 + 2]), "r"(pw[c8 * 4 + 3])
+                             : "memory");
+            }
+            tc::fence_async_smem();                  // P is read by the tensor cores (async proxy)
+            tc::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(bar_p);
+        }
+        wait_bar(bar_empty + ((n_tiles - 1) % NS) * 8, ((n_tiles - 1) / NS) & 1);
+        tc::tc_fence_after();
+
+        // ---- row sum = the two halves (exchanged through the idle P tile); store ----
+        float* s_half = reinterpret_cast<float*>(smem + G::kOffP);      // [2][128]
+        s_half[hf * BM + row_l] = l_run;
+        asm volatile("bar.sync 1, %0;" ::"n"(kMlaTcSoftmaxThreads) : "memory");   // softmax warps only
+        const float l_tot = l_run + s_half[(hf ^ 1) * BM + row_l];
+        const bool final_out = p.splits == 1;
+        const float inv = final_out ? (l_tot > 0.f ? 1.f / l_tot : 0.f) : 1.f;
+        float* pacc = final_out ? nullptr : p.part_acc + (grow * p.splits + chunk) * kMlaTcDc + col0;
+#pragma unroll
+        for (int c0 = hf * 128; c0 < (hf + 1) * 128; c0 += 32) {
+            uint32_t o[32];
+            tc::tmem_ld32(tmem_o + lane_sel + c0, o);
+            tc::tmem_ld_wait();
+            if (g < R && alive) {
+                if (final_out) {
+                    uint4* dst = reinterpret_cast<uint4*>(op + grow * kMlaTcDc + col0 + c0);
+#pragma unroll
+                    for (int c8 = 0; c8 < 4; ++c8) {
+                        uint4 v;
+                        v.x = Ops::pack(__uint_as_float(o[c8 * 8 + 0]) * inv, __uint_as_float(o[c8 * 8 + 1]) * inv);
+                        v.y = Ops::pack(__uint_as_float(o[c8 * 8 + 2]) * inv, __uint_as_float(o[c8 * 8 + 3]) * inv);
+                        v.z = Ops::pack(__uint_as_float(o[c8 * 8 + 4]) * inv, __uint_as_float(o[c8 * 8 + 5]) * inv);
+                        v.w = Ops::pack(__uint_as_float(o[c8 * 8 + 6]) * inv, __uint_as_float(o[c8 * 8 + 7]) * inv);
+                        dst[c8] = v;
+                    }
+                } else {
+                    uint4* dst = reinterpret_cast<uint4*>(pacc + c0);
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4)
+                        dst[c4] = make_uint4(o[c4 * 4], o[c4 * 4 + 1], o[c4 * 4 + 2], o[c4 * 4 + 3]);
+                }
+            }
+        }
+        if (!final_out && g < R && alive && rank == 0 && hf == 0) {
+            p.part_ml[(grow * p.splits + chunk) * 2] = m_run;
+            p.part_ml[(grow * p.splits + chunk) * 2 + 1] = l_tot;
+        }
     }
-    if (!final_out && g < R && alive && rank == 0 && hf == 0) {
-        p.part_ml[(grow * p.splits + chunk) * 2] = m_run;
-        p.part_ml[(grow * p.splits + chunk) * 2 + 1] = l_tot;
-    }
-    cp_async_wait<0>();
     tc::tc_fence_before();
     __syncthreads();
     if (warp == 0) tc::tmem_dealloc(tmem, kMlaTcTmemCols);

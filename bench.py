@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import sys
@@ -48,8 +49,14 @@ def parse_args():
     p.add_argument("--steps", type=int, default=200)
     p.add_argument("--warmup", type=int, default=20)
     p.add_argument("--impl", choices=["b200", "reference"], default="b200")
-    p.add_argument("--op", choices=["decode", "prefill"], default="decode",
-                   help="decode (the headline metric, default) or the dense prefill operator")
+    p.add_argument("--op", choices=["decode", "prefill", "mla"], default="decode",
+                   help="decode (the headline metric, default), the dense prefill operator, or "
+                        "paged latent (MLA) decode attention")
+    p.add_argument("--mla-workload", default="m2_deepseek_h128_bf16", choices=list(synth.MLA_WORKLOADS))
+    p.add_argument("--mla-kernel", default="auto", choices=["auto", "simt", "tcgen05"])
+    p.add_argument("--mla-stage", default="attend", choices=["attend", "decode"],
+                   help="attend: mla_latent_attention alone; decode: absorb + attention + value projection")
+    p.add_argument("--mla-splits", type=int, default=0)
     p.add_argument("--prefill-batch", type=int, default=4)
     p.add_argument("--prefill-seq", type=int, default=4096)
     p.add_argument("--prefill-kernel", default="auto", choices=["auto", "simt", "mma", "tcgen05"])
@@ -536,10 +543,104 @@ def run_prefill(args):
     print(json.dumps(line), flush=True)
 
 
+# --------------------------------------------------------------------------- MLA decode (secondary)
+def run_mla(args):
+    """Paged latent (MLA) decode attention: one JSON line with the achieved GB/s over the
+    algorithmic bytes (every visible cache row once, queries in, latent output back), the
+    roofline against the measured HBM peak (and the tensor-core time beside it: at 128 heads
+    the operator sits at the ridge), and the CPU restatement timed on a bounded sample."""
+    import attention_b200 as attn
+    from attention_b200.mla import mla_tc_status
+
+    if not torch.cuda.is_available() or not attn.is_cuda_extension_loaded():
+        raise RuntimeError("needs a CUDA device and the built C-ABI library (no CPU fallback)")
+    dev = torch.device("cuda", 0)
+    w = synth.MLA_WORKLOADS[args.mla_workload]
+    c = synth.make_mla_case(w, seed=args.seed, device=dev, cache_on_device=True)
+    scale = 1.0 / math.sqrt(w.dn + w.dr)
+    qa = attn.mla_query_absorb(c["q_nope"], c["w_uk"])
+
+    if args.mla_stage == "attend":
+        def step():
+            return attn.mla_latent_attention(qa, c["q_rope"], c["cache"], c["block_table"], c["lengths"],
+                                             c["positions"], scale=scale, kernel=args.mla_kernel,
+                                             splits=args.mla_splits)
+    else:
+        def step():
+            return attn.mla_decode(c["q_nope"], c["q_rope"], c["cache"], c["block_table"], c["lengths"],
+                                   c["positions"], c["w_uk"], c["w_uv"])
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    t0 = time.perf_counter()
+    while time.perf_counter() - t0 < args.spinup_seconds:
+        step()
+        torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(0))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with sampler:
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        sampler.sample()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    lens = c["lengths"].cpu()
+    nbytes = synth.mla_algorithmic_bytes(lens, w)
+    tokens = int(lens.to(torch.int64).sum())
+    flops = 2.0 * tokens * w.tq * w.heads * (w.dc + w.dr + w.dc)
+    gbps = nbytes / ms / 1e6
+    peak, src = measured_peak()
+    try:
+        tpeak = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"])
+    except (OSError, KeyError, ValueError):
+        tpeak = 1590.0
+    line = {
+        "metric": f"mla_{args.mla_stage}_gbps", "value": gbps, "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "dtype": str(w.dtype).replace("torch.", ""), "data": "synthetic", "vs_baseline": None,
+        "config": {"workload": w.name, "batch": w.batch, "tq": w.tq, "heads": w.heads, "dc": w.dc, "dr": w.dr,
+                   "page": w.page, "lengths": f"uniform[{w.len_lo},{w.len_hi}]", "kernel": args.mla_kernel,
+                   "stage": args.mla_stage, "bytes_per_step": nbytes, "flops_per_step": flops,
+                   "cache": "page pool larger than L2; no flush between steps"},
+        "roofline": {"bound": "hbm", "achieved": gbps, "peak": peak, "unit": "GB/s", "frac": gbps / peak,
+                     "peak_source": src, "traffic": None,
+                     "tensor_tflops": flops / ms / 1e9, "tensor_frac": flops / ms / 1e9 / tpeak},
+        "gpu_launches": args.steps * (3 if args.mla_stage == "attend" else 5), "clocks": sampler.summary(),
+        "tc_status": mla_tc_status(),
+    }
+    if not args.no_cpu_baseline:
+        from oracle import mla_oracle
+        n = 1                                   # bounded sample: the first sequence
+        sl = {k: (v[:n].cpu() if k in ("q_rope", "block_table", "lengths", "positions") else v.cpu())
+              for k, v in c.items() if k != "cache"}
+        used = int((int(lens[0]) + w.page - 1) // w.page)
+        pages = sl["block_table"][0, :used].long()
+        cache = c["cache"][pages.to(dev)].cpu()                     # only that sequence's pages
+        table = torch.arange(used, dtype=torch.int32).view(1, used)
+        threads = len(os.sched_getaffinity(0))
+        torch.set_num_threads(threads)
+        args_cpu = (qa[:n].cpu(), sl["q_rope"], cache, table, sl["lengths"], sl["positions"])
+        mla_oracle.reference_mla_latent_attention(*args_cpu, scale=scale)
+        t0 = time.perf_counter()
+        mla_oracle.reference_mla_latent_attention(*args_cpu, scale=scale)
+        dt = time.perf_counter() - t0
+        sample_bytes = synth.mla_algorithmic_bytes(lens[:n], synth.scaled_mla(w, batch=n))
+        line["cpu_baseline"] = {"value": sample_bytes / dt / 1e9, "unit": "GB/s", "cores": threads,
+                                "kind": "port", "seconds": dt,
+                                "sample": f"first sequence ({int(lens[0])} tokens), torch fp32 restatement "
+                                          "of the reference oracle (latent attention only)"}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
     if args.op == "prefill":
         run_prefill(args)
+        return
+    if args.op == "mla":
+        run_mla(args)
         return
     if args.impl == "reference":
         run_reference(args)
