@@ -15,25 +15,27 @@
 // distributed shared memory and adds what it receives, so both CTAs hold the same scores bit
 // for bit (a + b == b + a) and take the same softmax decisions without further talk.
 //
-// Per CTA: Q_r (80 KB), a five-stage ring of 32-token tiles (20 KB each), the P tile, and the
-// 16 KB landing buffer for the peer's partial scores: 212 KB, one CTA per SM.  TMEM: three score
-// buffers of 32 columns and 256 columns of output.
+// Per CTA: Q_r (80 KB), a four-stage ring of 32-token tiles (20 KB each), two P tiles, and two
+// 16 KB landing buffers for the peer's partial scores: 224 KB, one CTA per SM.  TMEM: three score
+// buffers of 32 columns and 256 columns of output.  The exchange runs one tile ahead of the
+// softmax (tile j+1's partial scores are in flight while tile j is exponentiated), and Q.C^T is
+// issued two tiles ahead.
 //
-// Warp roles (416 threads):
+// Warp roles (352 threads):
 //   warps 0-7    softmax: two threads per query row (16 score columns each)
-//   warps 8-11   loaders: 16-byte cp.async of this CTA's blocks of each cache row, one page lookup
+//   warps 8-9    loaders: 16-byte cp.async of this CTA's blocks of each cache row, one page lookup
 //                per tile when the page size is a multiple of 32 tokens, else one per row
-//   warp 12      one lane issues every tcgen05.mma
+//   warp 10      one lane issues every tcgen05.mma
 // There is no CTA-wide barrier in the token loop; the hand-offs are mbarriers.  Every wait is
 // time-bounded: a wait that runs out marks the CTA dead and raises the status word, and the CTA
 // still walks the protocol to the end, so its peer is never left waiting and no CTA exits
 // while the other may still write into its memory.
-//   full[5]    128 loader arrivals (when their copies land)  tile is in its stage   -> MMA lane
-//   empty[5]   tcgen05.commit   P.C of the stage's tile is done: stage, P tile, O are free
+//   full[4]    64 loader arrivals (when their copies land)   tile is in its stage   -> MMA lane
+//   empty[4]   tcgen05.commit   P.C of the stage's tile is done: stage, P tile, O are free
 //   bar_s[3]   tcgen05.commit   partial scores of a tile are in TMEM                -> softmax
 //   bar_p      8 warp arrivals  P is in shared memory, scores read, O rescaled      -> MMA lane
-//   bar_x      transaction barrier: the peer's st.async stores complete its 16 KB per tile
-//   bar_free   8 remote warp arrivals   the peer has consumed what this CTA sent it
+//   bar_x[2]   transaction barriers: the peer's st.async stores complete 16 KB per tile
+//   bar_free[2] 8 remote warp arrivals   the peer has consumed a landing buffer of its own
 #pragma once
 
 #include <type_traits>
@@ -48,9 +50,9 @@ namespace gqa_b200 {
 constexpr int kMlaTcRows = 128;        // query rows (token x head) per CTA pair
 constexpr int kMlaTcBN = 32;           // tokens per tile
 constexpr int kMlaTcSoftmaxThreads = 256;
-constexpr int kMlaTcLoadThreads = 128;
+constexpr int kMlaTcLoadThreads = 64;
 constexpr int kMlaTcThreads = kMlaTcSoftmaxThreads + kMlaTcLoadThreads + 32;
-constexpr int kMlaTcStages = 5;
+constexpr int kMlaTcStages = 4;
 constexpr int kMlaTcSBufs = 3;
 constexpr int kMlaTcTmemCols = 512;
 constexpr int kMlaTcDc = 512;
@@ -64,11 +66,11 @@ struct MlaTcGeom {
     static constexpr int kTileBlockBytes = kMlaTcBN * 128;              // 4 KB
     static constexpr int kStageBytes = kBlocks * kTileBlockBytes;       // 20 KB
     static constexpr int kPBytes = kMlaTcRows * 128;                    // 16 KB (64 of 128 bytes per row used)
-    static constexpr int kXBytes = kMlaTcRows * kMlaTcBN * 4;           // 16 KB
+    static constexpr int kXBytes = kMlaTcRows * kMlaTcBN * 4;           // 16 KB, two of them
     static constexpr int kOffK = kQBytes;
     static constexpr int kOffP = kOffK + kMlaTcStages * kStageBytes;
-    static constexpr int kOffX = kOffP + kPBytes;
-    static constexpr int kSmemBytes = kOffX + kXBytes;                  // 217088
+    static constexpr int kOffX = kOffP + 2 * kPBytes;
+    static constexpr int kSmemBytes = kOffX + 2 * kXBytes;              // 229376
 };
 
 namespace tc {
@@ -102,6 +104,37 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 }
 __device__ __forceinline__ void mbar_arrive_remote_relaxed(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// packed fp32 pairs and the three-input maximum (sm_100): half the instructions of the scalar forms
+__device__ __forceinline__ void add2(float& a0, float& a1, float b0, float b1) {
+    asm("{\n\t.reg .b64 ra, rb;\n\t"
+        "mov.b64 ra, {%0, %1};\n\tmov.b64 rb, {%2, %3};\n\t"
+        "add.rn.f32x2 ra, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, ra;\n\t}"
+        : "+f"(a0), "+f"(a1) : "f"(b0), "f"(b1));
+}
+// (d0, d1) = (a0, a1) * b + c
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b, float c) {
+    asm("{\n\t.reg .b64 ra, rb, rc;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+        "fma.rn.f32x2 ra, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, ra;\n\t}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// one non-blocking test of a barrier phase
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -143,7 +176,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     constexpr int HC = BN / 2;                       // score columns per softmax thread
 
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ __align__(8) uint64_t s_bar[2 * NS + NSB + 3];
+    __shared__ __align__(8) uint64_t s_bar[2 * NS + NSB + 5];
     __shared__ uint32_t s_tmem;
     __shared__ int s_dead;
 
@@ -192,8 +225,8 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     const uint32_t bar_empty = tc::smem_u32(&s_bar[NS]);
     const uint32_t bar_s0 = tc::smem_u32(&s_bar[2 * NS]);
     const uint32_t bar_p = tc::smem_u32(&s_bar[2 * NS + NSB]);
-    const uint32_t bar_x = tc::smem_u32(&s_bar[2 * NS + NSB + 1]);
-    const uint32_t bar_free = tc::smem_u32(&s_bar[2 * NS + NSB + 2]);
+    const uint32_t bar_x = tc::smem_u32(&s_bar[2 * NS + NSB + 1]);      // [2], one per landing buffer
+    const uint32_t bar_free = tc::smem_u32(&s_bar[2 * NS + NSB + 3]);   // [2]
 
     if (warp == 0) { tc::tmem_alloc(tc::smem_u32(&s_tmem), kMlaTcTmemCols); tc::tmem_relinquish(); }
     if (tid == 0) {
@@ -202,10 +235,14 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
 #pragma unroll
         for (int i = 0; i < NSB; ++i) tc::mbar_init(bar_s0 + i * 8, 1);
         tc::mbar_init(bar_p, NT / 32);               // one arrival per softmax warp
-        tc::mbar_init(bar_x, 1);                     // one local arrival announcing the bytes per tile
-        tc::mbar_init(bar_free, NT / 32);            // one arrival per peer softmax warp
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            tc::mbar_init(bar_x + i * 8, 1);         // one local arrival announcing the bytes per tile
+            tc::mbar_init(bar_free + i * 8, NT / 32);   // one arrival per peer softmax warp
+        }
         tc::fence_mbar_init();
-        tc::mbar_arrive_expect_tx(bar_x, G::kXBytes);   // tile 0
+        tc::mbar_arrive_expect_tx(bar_x, G::kXBytes);                          // tile 0
+        if (n_tiles > 1) tc::mbar_arrive_expect_tx(bar_x + 8, G::kXBytes);     // tile 1
         s_dead = 0;
     }
     tc::tc_fence_before();
@@ -246,7 +283,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             }
         }
         // this thread's chunks of a tile: the same (row, 16-byte column) for every tile
-        constexpr int MAXC = BN * 40 / NL;           // 10 chunks per thread for rank 1, 8 for rank 0
+        constexpr int MAXC = BN * 40 / NL;           // 20 chunks per thread for rank 1, 16 for rank 0
         const int nchunk = BN * cpr / NL;
         uint32_t soff[MAXC], doff[MAXC];             // byte offsets in the cache page run / in the stage
 #pragma unroll
@@ -304,45 +341,69 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         if (lane == 0) {
             const uint32_t idesc_s = tc::idesc_f16(BM, BN, AB_TYPE);
             const uint32_t idesc_o = tc::idesc_f16(BM, 256, AB_TYPE) | tc::kIdescBMnMajor;
+            // Descriptors differ only in their start-address field ((address >> 4) in the low bits,
+            // no carry out of it below 256 KB), so each one is a base plus a compile-time offset:
+            // the issuing lane's instruction stream per MMA stays a handful of instructions.
+            const uint64_t dq0 = tc::smem_desc_sw128_kmajor(sq);
+            const uint64_t dk0 = tc::smem_desc_sw128_kmajor(sk);
+            const uint64_t dp0 = tc::smem_desc_sw128_kmajor(sp);
+            const uint64_t dv0 = tc::smem_desc_sw128_mnmajor(sk, G::kTileBlockBytes);
             // S_r(j) = Q_r C_r(j)^T into score buffer j % NSB
             auto issue_qk = [&](int j) {
-                const uint32_t st = sk + (j % NS) * G::kStageBytes;
+                const uint64_t dk = dk0 + (uint64_t)(((j % NS) * G::kStageBytes) >> 4);
                 const uint32_t d = tmem + (j % NSB) * BN;
-                for (int blk = 0; blk < nb; ++blk) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const uint64_t da = tc::smem_desc_sw128_kmajor(sq + blk * G::kQBlockBytes + k * 32);
-                        const uint64_t db = tc::smem_desc_sw128_kmajor(st + blk * G::kTileBlockBytes + k * 32);
-                        tc::mma_f16_ss(d, da, db, idesc_s, (blk | k) ? 1u : 0u);
+                for (int blk = 0; blk < G::kBlocks; ++blk) {
+                    if (blk < nb) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            tc::mma_f16_ss(d, dq0 + (uint64_t)((blk * G::kQBlockBytes + k * 32) >> 4),
+                                           dk + (uint64_t)((blk * G::kTileBlockBytes + k * 32) >> 4), idesc_s,
+                                           (blk | k) ? 1u : 0u);
                     }
                 }
                 tc::mma_commit(bar_s0 + (j % NSB) * 8);
             };
             // O_r += P C_r(j): the first four blocks of the stage, as an MN-major operand
             auto issue_pv = [&](int j) {
-                const uint32_t st = sk + (j % NS) * G::kStageBytes;
+                const uint64_t dv = dv0 + (uint64_t)(((j % NS) * G::kStageBytes) >> 4);
+                const uint64_t dp = dp0 + (uint64_t)(((j & 1) * G::kPBytes) >> 4);
 #pragma unroll
-                for (int k = 0; k < BN / 16; ++k) {
-                    const uint64_t da = tc::smem_desc_sw128_kmajor(sp + k * 32);
-                    const uint64_t db = tc::smem_desc_sw128_mnmajor(st + k * 2048, G::kTileBlockBytes);
-                    tc::mma_f16_ss(tmem_o, da, db, idesc_o, (j | k) ? 1u : 0u);
-                }
+                for (int k = 0; k < BN / 16; ++k)
+                    tc::mma_f16_ss(tmem_o, dp + (uint64_t)((k * 32) >> 4), dv + (uint64_t)((k * 2048) >> 4), idesc_o,
+                                   (j | k) ? 1u : 0u);
                 tc::mma_commit(bar_empty + (j % NS) * 8);
             };
             wait_bar(bar_full, 0);                   // Q and tile 0
             tc::fence_async_smem();
             tc::tc_fence_after();
             issue_qk(0);
+            if (n_tiles > 1) {
+                wait_bar(bar_full + 8, 0);
+                tc::fence_async_smem();
+                tc::tc_fence_after();
+                issue_qk(1);
+            }
             for (int j = 0; j < n_tiles; ++j) {
-                if (j + 1 < n_tiles) {               // scores one tile ahead; buffer (j+1)%3 was read in j-2
-                    wait_bar(bar_full + ((j + 1) % NS) * 8, ((j + 1) / NS) & 1);
+                // scores two tiles ahead (buffer (j+2)%3 held S(j-1), read before bar_p(j-2)); if the
+                // tile has not landed yet, P.C(j) goes first
+                bool ahead = j + 2 >= n_tiles;
+                const uint32_t fb = bar_full + ((j + 2) % NS) * 8, fp = ((j + 2) / NS) & 1;
+                if (!ahead && tc::mbar_test(fb, fp)) {
                     tc::fence_async_smem();
                     tc::tc_fence_after();
-                    issue_qk(j + 1);
+                    issue_qk(j + 2);
+                    ahead = true;
                 }
                 wait_bar(bar_p, j & 1);              // P(j) stored, S(j) read, O rescaled
                 tc::tc_fence_after();
                 issue_pv(j);
+                if (!ahead) {
+                    wait_bar(fb, fp);
+                    tc::fence_async_smem();
+                    tc::tc_fence_after();
+                    issue_qk(j + 2);
+                }
             }
         }
         __syncwarp();
@@ -356,53 +417,64 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         const int my_stop = min(my_end, t1);         // this row sees tokens [t0, my_stop) of the chunk
         float m_run = -INFINITY, l_run = 0.f;
 
-        for (int j = 0; j < n_tiles; ++j) {
-            // ---- this CTA's partial scores of tile j ----
-            wait_bar(bar_s0 + (j % NSB) * 8, (j / NSB) & 1);
+        // partial scores of tile t: TMEM -> registers -> this thread's 16 columns into landing
+        // buffer t & 1 of the peer (once the peer has consumed tile t - 2 from it)
+        auto fetch_and_send = [&](int t, uint32_t (&r)[32]) {
+            wait_bar(bar_s0 + (t % NSB) * 8, (t / NSB) & 1);
             tc::tc_fence_after();
-            uint32_t r[32];
-            tc::tmem_ld32(tmem + (j % NSB) * BN + lane_sel, r);
+            tc::tmem_ld32(tmem + (t % NSB) * BN + lane_sel, r);
             tc::tmem_ld_wait();
-            // ---- send this thread's 16 columns to the peer (once it has consumed the previous tile) ----
-            if (j > 0) wait_bar_cluster(bar_free, (j - 1) & 1);
+            if (t >= 2) wait_bar_cluster(bar_free + (t & 1) * 8, ((t >> 1) - 1) & 1);
+            const uint32_t dst = peer_sx + (t & 1) * G::kXBytes + row_l * 16, dbar = peer_bar_x + (t & 1) * 8;
+            if (hf == 0) {                           // warp-uniform: static register indices, no selects
 #pragma unroll
-            for (int q4 = 0; q4 < HC / 4; ++q4) {    // (register arrays are indexed statically: select by hf)
-                const int lo = q4 * 4, hi = HC + q4 * 4;
-                tc::st_async_v4(peer_sx + ((hf * (HC / 4) + q4) * BM + row_l) * 16, hf ? r[hi] : r[lo],
-                                hf ? r[hi + 1] : r[lo + 1], hf ? r[hi + 2] : r[lo + 2], hf ? r[hi + 3] : r[lo + 3],
-                                peer_bar_x);
+                for (int q4 = 0; q4 < HC / 4; ++q4)
+                    tc::st_async_v4(dst + q4 * (BM * 16), r[q4 * 4], r[q4 * 4 + 1], r[q4 * 4 + 2], r[q4 * 4 + 3], dbar);
+            } else {
+#pragma unroll
+                for (int q4 = HC / 4; q4 < HC / 2; ++q4)
+                    tc::st_async_v4(dst + q4 * (BM * 16), r[q4 * 4], r[q4 * 4 + 1], r[q4 * 4 + 2], r[q4 * 4 + 3], dbar);
             }
+        };
+        // one tile of the softmax; r holds this tile's partial scores, rn receives the next tile's
+        auto softmax_tile = [&](int j, uint32_t (&r)[32], uint32_t (&rn)[32]) {
+            // ---- the next tile's partial scores travel while this tile is processed ----
+            if (j + 1 < n_tiles) fetch_and_send(j + 1, rn);
 
             // ---- full scores = mine + the peer's ----
-            wait_bar(bar_x, j & 1);
-            // announce the next tile's bytes; they cannot land before every warp here has passed the
-            // wait above, because the peer sends only after all warps have released the buffer below
-            if (tid == 0 && j + 1 < n_tiles) tc::mbar_arrive_expect_tx(bar_x, G::kXBytes);
+            wait_bar(bar_x + (j & 1) * 8, (j >> 1) & 1);
+            // announce the bytes of tile j + 2 on the same barrier; they cannot land before every
+            // warp here has passed the wait above, because the peer sends them only after all
+            // warps have released the buffer below
+            if (tid == 0 && j + 2 < n_tiles) tc::mbar_arrive_expect_tx(bar_x + (j & 1) * 8, G::kXBytes);
             float s[BN];
 #pragma unroll
             for (int c4 = 0; c4 < BN / 4; ++c4) {
                 uint32_t x0, x1, x2, x3;
                 asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3)
-                             : "r"(sx + (c4 * BM + row_l) * 16) : "memory");
-                s[c4 * 4 + 0] = __uint_as_float(r[c4 * 4 + 0]) + __uint_as_float(x0);
-                s[c4 * 4 + 1] = __uint_as_float(r[c4 * 4 + 1]) + __uint_as_float(x1);
-                s[c4 * 4 + 2] = __uint_as_float(r[c4 * 4 + 2]) + __uint_as_float(x2);
-                s[c4 * 4 + 3] = __uint_as_float(r[c4 * 4 + 3]) + __uint_as_float(x3);
+                             : "r"(sx + (j & 1) * G::kXBytes + (c4 * BM + row_l) * 16) : "memory");
+                s[c4 * 4 + 0] = __uint_as_float(r[c4 * 4 + 0]); s[c4 * 4 + 1] = __uint_as_float(r[c4 * 4 + 1]);
+                s[c4 * 4 + 2] = __uint_as_float(r[c4 * 4 + 2]); s[c4 * 4 + 3] = __uint_as_float(r[c4 * 4 + 3]);
+                tc::add2(s[c4 * 4 + 0], s[c4 * 4 + 1], __uint_as_float(x0), __uint_as_float(x1));
+                tc::add2(s[c4 * 4 + 2], s[c4 * 4 + 3], __uint_as_float(x2), __uint_as_float(x3));
             }
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive_remote_relaxed(peer_bar_free);   // the peer may overwrite the buffer
+            if (lane == 0) tc::mbar_arrive_remote_relaxed(peer_bar_free + (j & 1) * 8);   // buffer released
             const int tok0 = t0 + j * BN;
             if (tok0 + BN > my_stop) {
 #pragma unroll
                 for (int c = 0; c < BN; ++c)
                     if (tok0 + c >= my_stop) s[c] = -INFINITY;
             }
-            float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;
+            float a0 = s[0], a1 = s[1], a2 = s[2], a3 = s[3];
 #pragma unroll
-            for (int c = 0; c < BN; c += 4) {
-                a0 = fmaxf(a0, s[c]); a1 = fmaxf(a1, s[c + 1]); a2 = fmaxf(a2, s[c + 2]); a3 = fmaxf(a3, s[c + 3]);
+            for (int c = 4; c < BN - 4; c += 8) {
+                a0 = tc::max3(a0, s[c], s[c + 1]); a1 = tc::max3(a1, s[c + 2], s[c + 3]);
+                a2 = tc::max3(a2, s[c + 4], s[c + 5]); a3 = tc::max3(a3, s[c + 6], s[c + 7]);
             }
-            const float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * p.scale_log2;
+            a0 = tc::max3(a0, s[BN - 4], s[BN - 3]);
+            a1 = tc::max3(a1, s[BN - 2], s[BN - 1]);
+            const float mx = fmaxf(tc::max3(a0, a1, a2), a3) * p.scale_log2;
             const bool need = mx > m_run + kRescaleSlack;
             float alpha = 1.f;
             if (need) {
@@ -414,21 +486,30 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             const float ref = m_run == -INFINITY ? 0.f : m_run;
             uint32_t pw[HC / 2];
             {
+                const float nref = -ref;
+                float e[HC];                         // this thread's half of the row, as exponents
+                if (hf == 0) {                       // warp-uniform: static register indices
+#pragma unroll
+                    for (int c = 0; c < HC; c += 2) tc::fma2(e[c], e[c + 1], s[c], s[c + 1], p.scale_log2, nref);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < HC; c += 2) tc::fma2(e[c], e[c + 1], s[HC + c], s[HC + c + 1], p.scale_log2, nref);
+                }
                 float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
                 for (int c = 0; c < HC; c += 2) {
-                    const float p0 = fast_exp2(fmaf(hf ? s[HC + c] : s[c], p.scale_log2, -ref));
-                    const float p1 = fast_exp2(fmaf(hf ? s[HC + c + 1] : s[c + 1], p.scale_log2, -ref));
-                    ps0 += p0; ps1 += p1;
+                    const float p0 = fast_exp2(e[c]), p1 = fast_exp2(e[c + 1]);
+                    tc::add2(ps0, ps1, p0, p1);
                     pw[c / 2] = Ops::pack(p0, p1);
                 }
                 l_run += ps0 + ps1;                  // this thread's half of the row sum
             }
 
-            // ---- P.C(j-1) is done: the P tile and O may be touched ----
-            if (j > 0) wait_bar(bar_empty + ((j - 1) % NS) * 8, ((j - 1) / NS) & 1);
-            tc::tc_fence_after();
+            // ---- P tile j & 1 is free once P.C(j-2) is done; O may be rescaled once P.C(j-1) is ----
+            if (j > 1) wait_bar(bar_empty + ((j - 2) % NS) * 8, ((j - 2) / NS) & 1);
             if (j > 0 && __any_sync(0xffffffffu, need)) {   // warp-uniform: TMEM ld/st are collective
+                wait_bar(bar_empty + ((j - 1) % NS) * 8, ((j - 1) / NS) & 1);
+                tc::tc_fence_after();
 #pragma unroll
                 for (int c0 = hf * 128; c0 < (hf + 1) * 128; c0 += 32) {
                     uint32_t o[32];
@@ -443,7 +524,8 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
 #pragma unroll
             for (int c8 = 0; c8 < HC / 8; ++c8) {
                 const int ch = hf * (HC / 8) + c8;
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(sp + row_l * 128 + ((ch ^ (row_l & 7)) << 4)),
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};"
+                             ::"r"(sp + (j & 1) * G::kPBytes + row_l * 128 + ((ch ^ (row_l & 7)) << 4)),
                              "r"(pw[c8 * 4 + 0]), "r"(pw[c8 * 4 + 1]), "r"(pw[c8 * 4 + 2]), "r"(pw[c8 * 4 + 3])
                              : "memory");
             }
@@ -451,6 +533,12 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             tc::tc_fence_before();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(bar_p);
+        };
+        uint32_t ra[32], rb[32];                     // ping-pong: no register copies between tiles
+        fetch_and_send(0, ra);
+        for (int j = 0; j < n_tiles; j += 2) {
+            softmax_tile(j, ra, rb);
+            if (j + 1 < n_tiles) softmax_tile(j + 1, rb, ra);
         }
         wait_bar(bar_empty + ((n_tiles - 1) % NS) * 8, ((n_tiles - 1) / NS) & 1);
         tc::tc_fence_after();
