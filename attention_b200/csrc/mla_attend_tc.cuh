@@ -12,14 +12,20 @@
 //   S_r[128 x 32]  = Q_r[128 x 64 nb] . C_r[32 x 64 nb]^T     partial scores over its columns
 //   O_r[128 x 256] += P[128 x 32] . C_r[32 x 256]             its half of the latent output
 // The full scores are S_0 + S_1: every thread sends its partial scores to the peer CTA through
-// distributed shared memory and adds what it receives, so both CTAs hold the same scores bit
-// for bit (a + b == b + a) and take the same softmax decisions without further talk.
+// distributed shared memory (st.async, completing a transaction barrier there) and adds what it
+// receives, so both CTAs hold the same scores bit for bit (a + b == b + a) and take the same
+// softmax decisions without further talk.
 //
-// Per CTA: Q_r (80 KB), a four-stage ring of 32-token tiles (20 KB each), two P tiles, and two
-// 16 KB landing buffers for the peer's partial scores: 224 KB, one CTA per SM.  TMEM: three score
-// buffers of 32 columns and 256 columns of output.  The exchange runs one tile ahead of the
-// softmax (tile j+1's partial scores are in flight while tile j is exponentiated), and Q.C^T is
-// issued two tiles ahead.
+// Both A operands live in tensor memory, not in shared memory: Q_r is written there once per
+// work item (tcgen05.st from registers), and P is written over the score buffer it was
+// computed from.  An MMA with 128 rows of A in shared memory re-reads 4 KB of A for every 32
+// tokens of B; that made the first version of this kernel shared-memory-bandwidth bound at
+// about a fifth of the HBM rate.  With A in TMEM an MMA reads only its B tile (the cache rows)
+// from shared memory, and shared memory holds nothing but cache tiles and the landing buffers.
+//
+// TMEM (512 columns): three score buffers of 32 columns (P(j) overwrites the first 16 columns
+// of S(j)), 256 columns of output, 160 columns of Q_r.  Shared memory: an eight-stage ring of
+// 32-token tiles (20 KB each) and two 16 KB landing buffers: 192 KB, one CTA per SM.
 //
 // Warp roles (352 threads):
 //   warps 0-7    softmax: two threads per query row (16 score columns each)
@@ -30,10 +36,10 @@
 // time-bounded: a wait that runs out marks the CTA dead and raises the status word, and the CTA
 // still walks the protocol to the end, so its peer is never left waiting and no CTA exits
 // while the other may still write into its memory.
-//   full[4]    64 loader arrivals (when their copies land)   tile is in its stage   -> MMA lane
-//   empty[4]   tcgen05.commit   P.C of the stage's tile is done: stage, P tile, O are free
+//   full[8]    64 loader arrivals (when their copies land)   tile is in its stage   -> MMA lane
+//   empty[8]   tcgen05.commit   P.C of the stage's tile is done: stage and O are free
 //   bar_s[3]   tcgen05.commit   partial scores of a tile are in TMEM                -> softmax
-//   bar_p      8 warp arrivals  P is in shared memory, scores read, O rescaled      -> MMA lane
+//   bar_p      8 warp arrivals  P is in TMEM, O rescaled                            -> MMA lane
 //   bar_x[2]   transaction barriers: the peer's st.async stores complete 16 KB per tile
 //   bar_free[2] 8 remote warp arrivals   the peer has consumed a landing buffer of its own
 #pragma once
@@ -52,7 +58,7 @@ constexpr int kMlaTcBN = 32;           // tokens per tile
 constexpr int kMlaTcSoftmaxThreads = 256;
 constexpr int kMlaTcLoadThreads = 64;
 constexpr int kMlaTcThreads = kMlaTcSoftmaxThreads + kMlaTcLoadThreads + 32;
-constexpr int kMlaTcStages = 4;
+constexpr int kMlaTcStages = 8;
 constexpr int kMlaTcSBufs = 3;
 constexpr int kMlaTcTmemCols = 512;
 constexpr int kMlaTcDc = 512;
@@ -61,16 +67,17 @@ constexpr int kMlaTcWidth = kMlaTcDc + kMlaTcDr;
 
 struct MlaTcGeom {
     static constexpr int kBlocks = 5;                                   // 128-byte column blocks (rank 1)
-    static constexpr int kQBlockBytes = kMlaTcRows * 128;               // 16 KB
-    static constexpr int kQBytes = kBlocks * kQBlockBytes;              // 80 KB
     static constexpr int kTileBlockBytes = kMlaTcBN * 128;              // 4 KB
     static constexpr int kStageBytes = kBlocks * kTileBlockBytes;       // 20 KB
-    static constexpr int kPBytes = kMlaTcRows * 128;                    // 16 KB (64 of 128 bytes per row used)
     static constexpr int kXBytes = kMlaTcRows * kMlaTcBN * 4;           // 16 KB, two of them
-    static constexpr int kOffK = kQBytes;
-    static constexpr int kOffP = kOffK + kMlaTcStages * kStageBytes;
-    static constexpr int kOffX = kOffP + 2 * kPBytes;
-    static constexpr int kSmemBytes = kOffX + 2 * kXBytes;              // 229376
+    static constexpr int kOffK = 0;
+    static constexpr int kOffX = kOffK + kMlaTcStages * kStageBytes;
+    static constexpr int kSmemBytes = kOffX + 2 * kXBytes;              // 196608
+    // tensor memory columns
+    static constexpr int kColS = 0;                                     // kMlaTcSBufs x 32
+    static constexpr int kColO = kMlaTcSBufs * kMlaTcBN;                // 256
+    static constexpr int kColQ = kColO + 256;                           // 160 (rank 0 uses 128)
+    static_assert(kColQ + kBlocks * 32 <= kMlaTcTmemCols, "TMEM budget");
 };
 
 namespace tc {
@@ -176,7 +183,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     constexpr int HC = BN / 2;                       // score columns per softmax thread
 
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ __align__(8) uint64_t s_bar[2 * NS + NSB + 5];
+    __shared__ __align__(8) uint64_t s_bar[2 * NS + NSB + 6];
     __shared__ uint32_t s_tmem;
     __shared__ int s_dead;
 
@@ -220,13 +227,14 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         if (tid == 0 && status) atomicExch(status, 3);
         return;
     }
-    const uint32_t sq = s_base, sk = s_base + G::kOffK, sp = s_base + G::kOffP, sx = s_base + G::kOffX;
+    const uint32_t sk = s_base + G::kOffK, sx = s_base + G::kOffX;
     const uint32_t bar_full = tc::smem_u32(&s_bar[0]);
     const uint32_t bar_empty = tc::smem_u32(&s_bar[NS]);
     const uint32_t bar_s0 = tc::smem_u32(&s_bar[2 * NS]);
     const uint32_t bar_p = tc::smem_u32(&s_bar[2 * NS + NSB]);
     const uint32_t bar_x = tc::smem_u32(&s_bar[2 * NS + NSB + 1]);      // [2], one per landing buffer
     const uint32_t bar_free = tc::smem_u32(&s_bar[2 * NS + NSB + 3]);   // [2]
+    const uint32_t bar_q = tc::smem_u32(&s_bar[2 * NS + NSB + 5]);
 
     if (warp == 0) { tc::tmem_alloc(tc::smem_u32(&s_tmem), kMlaTcTmemCols); tc::tmem_relinquish(); }
     if (tid == 0) {
@@ -235,6 +243,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
 #pragma unroll
         for (int i = 0; i < NSB; ++i) tc::mbar_init(bar_s0 + i * 8, 1);
         tc::mbar_init(bar_p, NT / 32);               // one arrival per softmax warp
+        tc::mbar_init(bar_q, NT / 32);
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             tc::mbar_init(bar_x + i * 8, 1);         // one local arrival announcing the bytes per tile
@@ -250,7 +259,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     tc::cluster_sync_all();                          // both CTAs' barriers exist before any remote arrival
     tc::tc_fence_after();
     const uint32_t tmem = s_tmem;
-    const uint32_t tmem_o = tmem + NSB * BN;
+    const uint32_t tmem_o = tmem + G::kColO, tmem_q = tmem + G::kColQ;
     bool alive = true;
 
     auto timed_out = [&]() {
@@ -269,19 +278,6 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         // =============================== loader warps ===============================
         const int lt = tid - NT;
         const int cpr = nb * 8;                      // 16-byte chunks of a row that this CTA owns
-        {   // Q_r: [block][128 rows][128 B], rides with tile 0 on full[0]
-            const T* qa = reinterpret_cast<const T*>(p.q);
-            const T* qr = reinterpret_cast<const T*>(p.qr);
-            for (int i = lt; i < BM * cpr; i += NL) {
-                const int row = i / cpr, c = i - row * cpr;
-                const bool valid = g0 + row < R;
-                const long long gr = (long long)b * R + (valid ? g0 + row : 0);
-                const int col = col0 + c * 8;
-                const T* src = col < kMlaTcDc ? qa + gr * kMlaTcDc + col : qr + gr * kMlaTcDr + (col - kMlaTcDc);
-                cp_async16<0>(sq + (c >> 3) * G::kQBlockBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4), src,
-                              valid ? 16 : 0, 0);
-            }
-        }
         // this thread's chunks of a tile: the same (row, 16-byte column) for every tile
         constexpr int MAXC = BN * 40 / NL;           // 20 chunks per thread for rank 1, 16 for rank 0
         const int nchunk = BN * cpr / NL;
@@ -344,11 +340,10 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             // Descriptors differ only in their start-address field ((address >> 4) in the low bits,
             // no carry out of it below 256 KB), so each one is a base plus a compile-time offset:
             // the issuing lane's instruction stream per MMA stays a handful of instructions.
-            const uint64_t dq0 = tc::smem_desc_sw128_kmajor(sq);
             const uint64_t dk0 = tc::smem_desc_sw128_kmajor(sk);
-            const uint64_t dp0 = tc::smem_desc_sw128_kmajor(sp);
             const uint64_t dv0 = tc::smem_desc_sw128_mnmajor(sk, G::kTileBlockBytes);
-            // S_r(j) = Q_r C_r(j)^T into score buffer j % NSB
+            // S_r(j) = Q_r C_r(j)^T into score buffer j % NSB; A = Q_r from tensor memory, 8 columns
+            // (16 elements) per step of the contraction
             auto issue_qk = [&](int j) {
                 const uint64_t dk = dk0 + (uint64_t)(((j % NS) * G::kStageBytes) >> 4);
                 const uint32_t d = tmem + (j % NSB) * BN;
@@ -357,24 +352,26 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
                     if (blk < nb) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            tc::mma_f16_ss(d, dq0 + (uint64_t)((blk * G::kQBlockBytes + k * 32) >> 4),
+                            tc::mma_f16_ts(d, tmem_q + blk * 32 + k * 8,
                                            dk + (uint64_t)((blk * G::kTileBlockBytes + k * 32) >> 4), idesc_s,
                                            (blk | k) ? 1u : 0u);
                     }
                 }
                 tc::mma_commit(bar_s0 + (j % NSB) * 8);
             };
-            // O_r += P C_r(j): the first four blocks of the stage, as an MN-major operand
+            // O_r += P C_r(j): A = P(j) from the first 16 columns of score buffer j % NSB, B = the first
+            // four blocks of the stage as an MN-major operand
             auto issue_pv = [&](int j) {
                 const uint64_t dv = dv0 + (uint64_t)(((j % NS) * G::kStageBytes) >> 4);
-                const uint64_t dp = dp0 + (uint64_t)(((j & 1) * G::kPBytes) >> 4);
+                const uint32_t pa = tmem + (j % NSB) * BN;
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k)
-                    tc::mma_f16_ss(tmem_o, dp + (uint64_t)((k * 32) >> 4), dv + (uint64_t)((k * 2048) >> 4), idesc_o,
-                                   (j | k) ? 1u : 0u);
+                    tc::mma_f16_ts(tmem_o, pa + k * 8, dv + (uint64_t)((k * 2048) >> 4), idesc_o, (j | k) ? 1u : 0u);
                 tc::mma_commit(bar_empty + (j % NS) * 8);
             };
-            wait_bar(bar_full, 0);                   // Q and tile 0
+            wait_bar(bar_q, 0);                      // Q_r is in tensor memory
+            tc::tc_fence_after();
+            wait_bar(bar_full, 0);                   // tile 0
             tc::fence_async_smem();
             tc::tc_fence_after();
             issue_qk(0);
@@ -416,6 +413,38 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         const int my_end = g < R ? mla_row_end(p, b, g / p.heads) : 0;
         const int my_stop = min(my_end, t1);         // this row sees tokens [t0, my_stop) of the chunk
         float m_run = -INFINITY, l_run = 0.f;
+
+        // ---- Q_r: global -> registers -> tensor memory.  This thread writes half of its row
+        //      (16 columns = 32 elements per step); rows past the last query row are zero ----
+        {
+            const T* qa = reinterpret_cast<const T*>(p.q) + grow * kMlaTcDc;
+            const T* qr = reinterpret_cast<const T*>(p.qr) + grow * kMlaTcDr;
+            const int per_thread = nb * 16;          // 32-bit columns per thread: 64 (rank 0) or 80 (rank 1)
+#pragma unroll
+            for (int st = 0; st < 5; ++st) {
+                if (st * 16 < per_thread) {
+                    const int e = hf * per_thread * 2 + st * 32;     // first element of this step
+                    const int col = col0 + e;                        // cache column it multiplies
+                    uint32_t w[16];
+                    if (g < R) {
+                        const uint4* src = reinterpret_cast<const uint4*>(col < kMlaTcDc ? qa + col : qr + (col - kMlaTcDc));
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            const uint4 v = __ldg(src + q4);
+                            w[q4 * 4] = v.x; w[q4 * 4 + 1] = v.y; w[q4 * 4 + 2] = v.z; w[q4 * 4 + 3] = v.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) w[c] = 0u;
+                    }
+                    tc::tmem_st16(tmem_q + lane_sel + hf * per_thread + st * 16, w);
+                }
+            }
+            tc::tmem_st_wait();
+            tc::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(bar_q);
+        }
 
         // partial scores of tile t: TMEM -> registers -> this thread's 16 columns into landing
         // buffer t & 1 of the peer (once the peer has consumed tile t - 2 from it)
@@ -505,8 +534,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
                 l_run += ps0 + ps1;                  // this thread's half of the row sum
             }
 
-            // ---- P tile j & 1 is free once P.C(j-2) is done; O may be rescaled once P.C(j-1) is ----
-            if (j > 1) wait_bar(bar_empty + ((j - 2) % NS) * 8, ((j - 2) / NS) & 1);
+            // ---- O may be rescaled once P.C(j-1) is done ----
             if (j > 0 && __any_sync(0xffffffffu, need)) {   // warp-uniform: TMEM ld/st are collective
                 wait_bar(bar_empty + ((j - 1) % NS) * 8, ((j - 1) / NS) & 1);
                 tc::tc_fence_after();
@@ -519,17 +547,12 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
                     for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
                     tc::tmem_st32(tmem_o + lane_sel + c0, o);
                 }
-                tc::tmem_st_wait();
             }
-#pragma unroll
-            for (int c8 = 0; c8 < HC / 8; ++c8) {
-                const int ch = hf * (HC / 8) + c8;
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};"
-                             ::"r"(sp + (j & 1) * G::kPBytes + row_l * 128 + ((ch ^ (row_l & 7)) << 4)),
-                             "r"(pw[c8 * 4 + 0]), "r"(pw[c8 * 4 + 1]), "r"(pw[c8 * 4 + 2]), "r"(pw[c8 * 4 + 3])
-                             : "memory");
-            }
-            tc::fence_async_smem();                  // P is read by the tensor cores (async proxy)
+            // ---- P(j) goes over the first 16 columns of S(j): every warp has read S(j) once the
+            //      previous tile's P is complete (a warp fetches S(j) before it arrives for tile j-1) ----
+            if (j > 0) wait_bar(bar_p, (j - 1) & 1);
+            tc::tmem_st8(tmem + (j % NSB) * BN + lane_sel + hf * (HC / 2), pw);
+            tc::tmem_st_wait();
             tc::tc_fence_before();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(bar_p);
@@ -543,8 +566,8 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         wait_bar(bar_empty + ((n_tiles - 1) % NS) * 8, ((n_tiles - 1) / NS) & 1);
         tc::tc_fence_after();
 
-        // ---- row sum = the two halves (exchanged through the idle P tile); store ----
-        float* s_half = reinterpret_cast<float*>(smem + G::kOffP);      // [2][128]
+        // ---- row sum = the two halves (exchanged through an idle landing buffer); store ----
+        float* s_half = reinterpret_cast<float*>(smem + G::kOffX);      // [2][128], landing buffer 0 is idle
         s_half[hf * BM + row_l] = l_run;
         asm volatile("bar.sync 1, %0;" ::"n"(kMlaTcSoftmaxThreads) : "memory");   // softmax warps only
         const float l_tot = l_run + s_half[(hf ^ 1) * BM + row_l];
