@@ -23,9 +23,14 @@
 // about a fifth of the HBM rate.  With A in TMEM an MMA reads only its B tile (the cache rows)
 // from shared memory, and shared memory holds nothing but cache tiles and the landing buffers.
 //
-// TMEM (512 columns): three score buffers of 32 columns (P(j) overwrites the first 16 columns
-// of S(j)), 256 columns of output, 160 columns of Q_r.  Shared memory: an eight-stage ring of
-// 32-token tiles (20 KB each) and two 16 KB landing buffers: 192 KB, one CTA per SM.
+// An MMA costs its issuing lane about 70 cycles whatever its width, so the scores of two
+// 32-token tiles are computed by one set of 64-wide MMAs (the ring keeps consecutive tiles
+// adjacent); everything else works per 32-token tile.
+//
+// TMEM (512 columns): four score buffers of 32 columns (P(j) overwrites the first 16 columns
+// of S(j)), 256 columns of output, 128 columns for the latent part of Q_r.  Shared memory: an
+// eight-stage ring of 32-token tiles (20 KB each), the rotated block of Q_r (16 KB, rank 1) and
+// two 16 KB landing buffers: 208 KB, one CTA per SM.
 //
 // Warp roles (352 threads):
 //   warps 0-7    softmax: two threads per query row (16 score columns each)
@@ -38,7 +43,7 @@
 // while the other may still write into its memory.
 //   full[8]    64 loader arrivals (when their copies land)   tile is in its stage   -> MMA lane
 //   empty[8]   tcgen05.commit   P.C of the stage's tile is done: stage and O are free
-//   bar_s[3]   tcgen05.commit   partial scores of a tile are in TMEM                -> softmax
+//   bar_s[4]   tcgen05.commit   partial scores of a tile are in TMEM                -> softmax
 //   bar_p      8 warp arrivals  P is in TMEM, O rescaled                            -> MMA lane
 //   bar_x[2]   transaction barriers: the peer's st.async stores complete 16 KB per tile
 //   bar_free[2] 8 remote warp arrivals   the peer has consumed a landing buffer of its own
@@ -59,7 +64,7 @@ constexpr int kMlaTcSoftmaxThreads = 256;
 constexpr int kMlaTcLoadThreads = 64;
 constexpr int kMlaTcThreads = kMlaTcSoftmaxThreads + kMlaTcLoadThreads + 32;
 constexpr int kMlaTcStages = 8;
-constexpr int kMlaTcSBufs = 3;
+constexpr int kMlaTcSBufs = 4;           // two pairs of score buffers
 constexpr int kMlaTcTmemCols = 512;
 constexpr int kMlaTcDc = 512;
 constexpr int kMlaTcDr = 64;
@@ -67,17 +72,22 @@ constexpr int kMlaTcWidth = kMlaTcDc + kMlaTcDr;
 
 struct MlaTcGeom {
     static constexpr int kBlocks = 5;                                   // 128-byte column blocks (rank 1)
-    static constexpr int kTileBlockBytes = kMlaTcBN * 128;              // 4 KB
-    static constexpr int kStageBytes = kBlocks * kTileBlockBytes;       // 20 KB
+    static constexpr int kTileBlockBytes = kMlaTcBN * 128;              // 4 KB: one tile's rows of one block
+    // the ring is laid out [block][stage][32 rows][128 B], so that two consecutive tiles are 64
+    // consecutive rows of every block and one MMA can take both as its B operand
+    static constexpr int kBlockRegion = kMlaTcStages * kTileBlockBytes; // 32 KB
+    static constexpr int kQRopeBytes = kMlaTcRows * 128;                // 16 KB: rotated query block (rank 1)
     static constexpr int kXBytes = kMlaTcRows * kMlaTcBN * 4;           // 16 KB, two of them
     static constexpr int kOffK = 0;
-    static constexpr int kOffX = kOffK + kMlaTcStages * kStageBytes;
-    static constexpr int kSmemBytes = kOffX + 2 * kXBytes;              // 196608
+    static constexpr int kOffQr = kOffK + kBlocks * kBlockRegion;
+    static constexpr int kOffX = kOffQr + kQRopeBytes;
+    static constexpr int kSmemBytes = kOffX + 2 * kXBytes;              // 212992
     // tensor memory columns
     static constexpr int kColS = 0;                                     // kMlaTcSBufs x 32
     static constexpr int kColO = kMlaTcSBufs * kMlaTcBN;                // 256
-    static constexpr int kColQ = kColO + 256;                           // 160 (rank 0 uses 128)
-    static_assert(kColQ + kBlocks * 32 <= kMlaTcTmemCols, "TMEM budget");
+    static constexpr int kColQ = kColO + 256;                           // 128: the latent part of Q_r
+    static_assert(kColQ + 4 * 32 <= kMlaTcTmemCols, "TMEM budget");
+    static_assert(kMlaTcStages % 2 == 0 && kMlaTcSBufs % 2 == 0, "tiles are issued in pairs");
 };
 
 namespace tc {
@@ -227,7 +237,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         if (tid == 0 && status) atomicExch(status, 3);
         return;
     }
-    const uint32_t sk = s_base + G::kOffK, sx = s_base + G::kOffX;
+    const uint32_t sk = s_base + G::kOffK, sqr = s_base + G::kOffQr, sx = s_base + G::kOffX;
     const uint32_t bar_full = tc::smem_u32(&s_bar[0]);
     const uint32_t bar_empty = tc::smem_u32(&s_bar[NS]);
     const uint32_t bar_s0 = tc::smem_u32(&s_bar[2 * NS]);
@@ -278,6 +288,15 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         // =============================== loader warps ===============================
         const int lt = tid - NT;
         const int cpr = nb * 8;                      // 16-byte chunks of a row that this CTA owns
+        if (rank) {   // the rotated block of Q_r stays in shared memory: [128 rows][128 B], rides on full[0]
+            const T* qr = reinterpret_cast<const T*>(p.qr);
+            for (int i = lt; i < BM * 8; i += NL) {
+                const int row = i >> 3, c = i & 7;
+                const bool valid = g0 + row < R;
+                const T* src = qr + ((long long)b * R + (valid ? g0 + row : 0)) * kMlaTcDr + c * 8;
+                cp_async16<0>(sqr + row * 128 + ((c ^ (row & 7)) << 4), src, valid ? 16 : 0, 0);
+            }
+        }
         // this thread's chunks of a tile: the same (row, 16-byte column) for every tile
         constexpr int MAXC = BN * 40 / NL;           // 20 chunks per thread for rank 1, 16 for rank 0
         const int nchunk = BN * cpr / NL;
@@ -287,7 +306,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             const int i = lt + k * NL;
             const int row = i / cpr, c = i - row * cpr;
             soff[k] = (uint32_t)(row * kMlaTcWidth + col0 + c * 8) * 2u;
-            doff[k] = (uint32_t)((c >> 3) * G::kTileBlockBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4));
+            doff[k] = (uint32_t)((c >> 3) * G::kBlockRegion + row * 128 + (((c & 7) ^ (row & 7)) << 4));
         }
         const char* cache = reinterpret_cast<const char*>(p.cache);
         const int32_t* trow = p.table + (long long)b * p.max_pages;
@@ -296,7 +315,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         for (int j = 0; j < n_tiles; ++j) {
             const int stage = j % NS;
             if (j >= NS) wait_bar(bar_empty + stage * 8, ((j / NS) - 1) & 1);
-            const uint32_t st = sk + stage * G::kStageBytes;
+            const uint32_t st = sk + stage * G::kTileBlockBytes;
             const int tok0 = t0 + j * BN;
             if (page_run) {
                 const int pg = tok0 >> p.page_shift;
@@ -335,72 +354,75 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     } else if (is_mma) {
         // =============================== MMA warp: one lane issues everything ===============================
         if (lane == 0) {
-            const uint32_t idesc_s = tc::idesc_f16(BM, BN, AB_TYPE);
+            const uint32_t idesc_s1 = tc::idesc_f16(BM, BN, AB_TYPE);        // one tile
+            const uint32_t idesc_s2 = tc::idesc_f16(BM, 2 * BN, AB_TYPE);    // a pair of tiles
             const uint32_t idesc_o = tc::idesc_f16(BM, 256, AB_TYPE) | tc::kIdescBMnMajor;
             // Descriptors differ only in their start-address field ((address >> 4) in the low bits,
-            // no carry out of it below 256 KB), so each one is a base plus a compile-time offset:
-            // the issuing lane's instruction stream per MMA stays a handful of instructions.
+            // no carry out of it below 256 KB), so each one is a base plus a small offset: the
+            // issuing lane's instruction stream per MMA stays a handful of instructions.
             const uint64_t dk0 = tc::smem_desc_sw128_kmajor(sk);
-            const uint64_t dv0 = tc::smem_desc_sw128_mnmajor(sk, G::kTileBlockBytes);
-            // S_r(j) = Q_r C_r(j)^T into score buffer j % NSB; A = Q_r from tensor memory, 8 columns
-            // (16 elements) per step of the contraction
-            auto issue_qk = [&](int j) {
-                const uint64_t dk = dk0 + (uint64_t)(((j % NS) * G::kStageBytes) >> 4);
+            const uint64_t dqr0 = tc::smem_desc_sw128_kmajor(sqr);
+            const uint64_t dv0 = tc::smem_desc_sw128_mnmajor(sk, G::kBlockRegion);
+            // Partial scores of tiles j and j+1 (or of tile j alone) in one set of MMAs: an MMA costs
+            // the issuing lane about 70 cycles whatever its width, so the pair halves that cost per
+            // token.  j is even, so the two stages and the two score buffers are adjacent.  A = the
+            // latent part of Q_r from tensor memory (8 columns = 16 elements per step) and, on
+            // rank 1, its rotated block from shared memory.
+            auto issue_qk = [&](int j, bool pair) {
+                const uint64_t dk = dk0 + (uint64_t)(((j % NS) * G::kTileBlockBytes) >> 4);
                 const uint32_t d = tmem + (j % NSB) * BN;
+                const uint32_t idesc = pair ? idesc_s2 : idesc_s1;
 #pragma unroll
-                for (int blk = 0; blk < G::kBlocks; ++blk) {
-                    if (blk < nb) {
+                for (int blk = 0; blk < 4; ++blk) {
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            tc::mma_f16_ts(d, tmem_q + blk * 32 + k * 8,
-                                           dk + (uint64_t)((blk * G::kTileBlockBytes + k * 32) >> 4), idesc_s,
-                                           (blk | k) ? 1u : 0u);
-                    }
+                    for (int k = 0; k < 4; ++k)
+                        tc::mma_f16_ts(d, tmem_q + blk * 32 + k * 8,
+                                       dk + (uint64_t)((blk * G::kBlockRegion + k * 32) >> 4), idesc, (blk | k) ? 1u : 0u);
+                }
+                if (rank) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        tc::mma_f16_ss(d, dqr0 + (uint64_t)((k * 32) >> 4),
+                                       dk + (uint64_t)((4 * G::kBlockRegion + k * 32) >> 4), idesc, 1u);
                 }
                 tc::mma_commit(bar_s0 + (j % NSB) * 8);
+                if (pair) tc::mma_commit(bar_s0 + ((j + 1) % NSB) * 8);
             };
             // O_r += P C_r(j): A = P(j) from the first 16 columns of score buffer j % NSB, B = the first
             // four blocks of the stage as an MN-major operand
             auto issue_pv = [&](int j) {
-                const uint64_t dv = dv0 + (uint64_t)(((j % NS) * G::kStageBytes) >> 4);
+                const uint64_t dv = dv0 + (uint64_t)(((j % NS) * G::kTileBlockBytes) >> 4);
                 const uint32_t pa = tmem + (j % NSB) * BN;
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k)
                     tc::mma_f16_ts(tmem_o, pa + k * 8, dv + (uint64_t)((k * 2048) >> 4), idesc_o, (j | k) ? 1u : 0u);
                 tc::mma_commit(bar_empty + (j % NS) * 8);
             };
-            wait_bar(bar_q, 0);                      // Q_r is in tensor memory
-            tc::tc_fence_after();
-            wait_bar(bar_full, 0);                   // tile 0
-            tc::fence_async_smem();
-            tc::tc_fence_after();
-            issue_qk(0);
-            if (n_tiles > 1) {
-                wait_bar(bar_full + 8, 0);
+            // wait for the tiles of the pair starting at tile j to land, then issue their scores
+            auto scores_of_pair = [&](int j) {
+                const bool pair = j + 1 < n_tiles;
+                wait_bar(bar_full + (j % NS) * 8, (j / NS) & 1);
+                if (pair) wait_bar(bar_full + ((j + 1) % NS) * 8, ((j + 1) / NS) & 1);
                 tc::fence_async_smem();
                 tc::tc_fence_after();
-                issue_qk(1);
-            }
-            for (int j = 0; j < n_tiles; ++j) {
-                // scores two tiles ahead (buffer (j+2)%3 held S(j-1), read before bar_p(j-2)); if the
-                // tile has not landed yet, P.C(j) goes first
-                bool ahead = j + 2 >= n_tiles;
-                const uint32_t fb = bar_full + ((j + 2) % NS) * 8, fp = ((j + 2) / NS) & 1;
-                if (!ahead && tc::mbar_test(fb, fp)) {
-                    tc::fence_async_smem();
-                    tc::tc_fence_after();
-                    issue_qk(j + 2);
-                    ahead = true;
-                }
-                wait_bar(bar_p, j & 1);              // P(j) stored, S(j) read, O rescaled
+                issue_qk(j, pair);
+            };
+            wait_bar(bar_q, 0);                      // Q_r is in tensor memory
+            tc::tc_fence_after();
+            scores_of_pair(0);                       // (the rotated block of Q_r rides on full[0])
+            if (n_tiles > 2) scores_of_pair(2);
+            for (int j = 0; j < n_tiles; j += 2) {
+                wait_bar(bar_p, j & 1);              // P(j) is in tensor memory, O rescaled
                 tc::tc_fence_after();
                 issue_pv(j);
-                if (!ahead) {
-                    wait_bar(fb, fp);
-                    tc::fence_async_smem();
+                if (j + 1 < n_tiles) {
+                    wait_bar(bar_p, (j + 1) & 1);
                     tc::tc_fence_after();
-                    issue_qk(j + 2);
+                    issue_pv(j + 1);
                 }
+                // the pair after next reuses this pair's score buffers: P.C(j), P.C(j+1) are queued
+                // ahead of it and the tensor pipe runs in order
+                if (j + 4 < n_tiles) scores_of_pair(j + 4);
             }
         }
         __syncwarp();
@@ -414,31 +436,25 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         const int my_stop = min(my_end, t1);         // this row sees tokens [t0, my_stop) of the chunk
         float m_run = -INFINITY, l_run = 0.f;
 
-        // ---- Q_r: global -> registers -> tensor memory.  This thread writes half of its row
-        //      (16 columns = 32 elements per step); rows past the last query row are zero ----
+        // ---- latent part of Q_r: global -> registers -> tensor memory.  This thread writes half of
+        //      its row (16 columns = 32 elements per step); rows past the last query row are zero ----
         {
-            const T* qa = reinterpret_cast<const T*>(p.q) + grow * kMlaTcDc;
-            const T* qr = reinterpret_cast<const T*>(p.qr) + grow * kMlaTcDr;
-            const int per_thread = nb * 16;          // 32-bit columns per thread: 64 (rank 0) or 80 (rank 1)
+            const T* qa = reinterpret_cast<const T*>(p.q) + grow * kMlaTcDc + col0 + hf * 128;
 #pragma unroll
-            for (int st = 0; st < 5; ++st) {
-                if (st * 16 < per_thread) {
-                    const int e = hf * per_thread * 2 + st * 32;     // first element of this step
-                    const int col = col0 + e;                        // cache column it multiplies
-                    uint32_t w[16];
-                    if (g < R) {
-                        const uint4* src = reinterpret_cast<const uint4*>(col < kMlaTcDc ? qa + col : qr + (col - kMlaTcDc));
+            for (int st = 0; st < 4; ++st) {
+                uint32_t w[16];
+                if (g < R) {
+                    const uint4* src = reinterpret_cast<const uint4*>(qa + st * 32);
 #pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {
-                            const uint4 v = __ldg(src + q4);
-                            w[q4 * 4] = v.x; w[q4 * 4 + 1] = v.y; w[q4 * 4 + 2] = v.z; w[q4 * 4 + 3] = v.w;
-                        }
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) w[c] = 0u;
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const uint4 v = __ldg(src + q4);
+                        w[q4 * 4] = v.x; w[q4 * 4 + 1] = v.y; w[q4 * 4 + 2] = v.z; w[q4 * 4 + 3] = v.w;
                     }
-                    tc::tmem_st16(tmem_q + lane_sel + hf * per_thread + st * 16, w);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) w[c] = 0u;
                 }
+                tc::tmem_st16(tmem_q + lane_sel + hf * 64 + st * 16, w);
             }
             tc::tmem_st_wait();
             tc::tc_fence_before();
