@@ -136,7 +136,9 @@ int launch_attend_simt(const MlaParams& p, cudaStream_t stream) {
     else rc = go(mla_attend_simt_kernel<T, 16>);
     if (rc != 0) return rc;
     if (p.splits > 1) {
-        mla_merge_kernel<T><<<(unsigned)(rows * p.heads), 128, 0, stream>>>(p);
+        const long long total = rows * p.heads;
+        mla_merge_kernel<T><<<(unsigned)((total + kMlaMergeWarps - 1) / kMlaMergeWarps), kMlaMergeWarps * 32, 0,
+                              stream>>>(p, total);
         rc = (int)cudaGetLastError();
     }
     return rc;
@@ -163,7 +165,9 @@ int launch_attend_tc(const MlaParams& p, cudaStream_t stream) {
     int rc = (int)cudaGetLastError();
     if (rc != 0) return rc;
     if (p.splits > 1) {
-        mla_merge_kernel<T><<<(unsigned)((long long)p.batch * R), 128, 0, stream>>>(p);
+        const long long total = (long long)p.batch * R;
+        mla_merge_kernel<T><<<(unsigned)((total + kMlaMergeWarps - 1) / kMlaMergeWarps), kMlaMergeWarps * 32, 0,
+                              stream>>>(p, total);
         rc = (int)cudaGetLastError();
     }
     return rc;
@@ -180,8 +184,7 @@ int launch_project(const void* x, const void* w, void* out, long long rows, int 
         mla_absorb_kernel<T><<<grid, kProjThreads, smem, stream>>>(
             static_cast<const T*>(x), static_cast<const T*>(w), static_cast<T*>(out), rows, heads, d_in, d_out);
     } else {
-        const int per_cta = (kProjThreads / 32) * 8;
-        const dim3 grid(chunks, (unsigned)((d_out + per_cta - 1) / per_cta), (unsigned)heads);
+        const dim3 grid(chunks, (unsigned)((d_out + kProjThreads - 1) / kProjThreads), (unsigned)heads);
         mla_value_kernel<T><<<grid, kProjThreads, smem, stream>>>(
             static_cast<const T*>(x), static_cast<const T*>(w), static_cast<T*>(out), rows, heads, d_in, d_out);
     }

@@ -167,13 +167,18 @@ mla_attend_simt_kernel(const MlaParams p) {
     }
 }
 
-// One CTA per (row, head): fold the splits against their global maximum.
+// One warp per (row, head): fold the splits against their global maximum.  Lanes read the
+// partial sums as float4 (dc a multiple of 4) or scalars; the order of the sum over splits is
+// fixed, so the result does not depend on the launch shape.
+constexpr int kMlaMergeWarps = 4;
 template <typename T>
-__global__ void __launch_bounds__(128)
-mla_merge_kernel(const MlaParams p) {
+__global__ void __launch_bounds__(kMlaMergeWarps * 32)
+mla_merge_kernel(const MlaParams p, long long total) {
     pdl_launch_dependents();
     pdl_wait();
-    const long long rh = blockIdx.x;
+    const int lane = threadIdx.x & 31;
+    const long long rh = (long long)blockIdx.x * kMlaMergeWarps + (threadIdx.x >> 5);
+    if (rh >= total) return;
     const float* ml = p.part_ml + rh * p.splits * 2;
     float mx = -INFINITY;
     for (int s = 0; s < p.splits; ++s)
@@ -183,20 +188,54 @@ mla_merge_kernel(const MlaParams p) {
         if (ml[2 * s + 1] > 0.f) sum += fast_exp2(ml[2 * s] - mx) * ml[2 * s + 1];
     const float inv = sum > 0.f ? 1.f / sum : 0.f;
     T* op = reinterpret_cast<T*>(p.out) + rh * p.dc;
-    for (int d = threadIdx.x; d < p.dc; d += blockDim.x) {
-        float a = 0.f;
-        for (int s = 0; s < p.splits; ++s)
-            if (ml[2 * s + 1] > 0.f)
-                a += fast_exp2(ml[2 * s] - mx) * p.part_acc[(rh * p.splits + s) * p.dc + d];
-        op[d] = from_f32<T>(a * inv);
+    const float* acc = p.part_acc + rh * p.splits * p.dc;
+    if ((p.dc & 3) == 0) {
+        for (int d = lane * 4; d < p.dc; d += 128) {
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < p.splits; ++s) {
+                if (ml[2 * s + 1] > 0.f) {
+                    const float w = fast_exp2(ml[2 * s] - mx);
+                    const float4 x = *reinterpret_cast<const float4*>(acc + (long long)s * p.dc + d);
+                    a.x += w * x.x; a.y += w * x.y; a.z += w * x.z; a.w += w * x.w;
+                }
+            }
+            op[d] = from_f32<T>(a.x * inv); op[d + 1] = from_f32<T>(a.y * inv);
+            op[d + 2] = from_f32<T>(a.z * inv); op[d + 3] = from_f32<T>(a.w * inv);
+        }
+    } else {
+        for (int d = lane; d < p.dc; d += 32) {
+            float a = 0.f;
+            for (int s = 0; s < p.splits; ++s)
+                if (ml[2 * s + 1] > 0.f) a += fast_exp2(ml[2 * s] - mx) * acc[(long long)s * p.dc + d];
+            op[d] = from_f32<T>(a * inv);
+        }
     }
 }
 
 // ---------------------------------------------------------------------------
 // per-head projections
 // ---------------------------------------------------------------------------
-constexpr int kProjRows = 8;          // rows of x per CTA
+constexpr int kProjRows = 16;         // rows of x per CTA
 constexpr int kProjThreads = 128;
+
+// x rows of one head into shared memory as [d_in][kProjRows] fp32 (rows innermost, so that a
+// thread reads all rows of one contraction index with four 16-byte loads)
+template <typename T>
+__device__ __forceinline__ void proj_stage_x(float* s_x, const T* __restrict__ x, long long r0, int nr, int heads,
+                                             int h, int d_in) {
+    for (int i = threadIdx.x; i < kProjRows * d_in; i += kProjThreads) {
+        const int rr = i / d_in, j = i - rr * d_in;       // coalesced along j
+        s_x[j * kProjRows + rr] = rr < nr ? to_f32(x[((r0 + rr) * heads + h) * d_in + j]) : 0.f;
+    }
+}
+__device__ __forceinline__ void proj_fma_rows(float (&acc)[kProjRows], const float* s_xj, float wv) {
+#pragma unroll
+    for (int q = 0; q < kProjRows / 4; ++q) {
+        const float4 xv = *reinterpret_cast<const float4*>(s_xj + q * 4);
+        acc[q * 4 + 0] += xv.x * wv; acc[q * 4 + 1] += xv.y * wv;
+        acc[q * 4 + 2] += xv.z * wv; acc[q * 4 + 3] += xv.w * wv;
+    }
+}
 
 // out[r, h, c] = sum_j x[r, h, j] * w[h, j, c]: one thread per output column,
 // weights read coalesced along c.  grid (row chunks, column tiles, heads).
@@ -204,16 +243,13 @@ template <typename T>
 __global__ void __launch_bounds__(kProjThreads)
 mla_absorb_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ out,
                   long long rows, int heads, int d_in, int d_out) {
-    extern __shared__ __align__(16) float s_x[];      // [kProjRows][d_in]
+    extern __shared__ __align__(16) float s_x[];      // [d_in][kProjRows]
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.z;
     const long long r0 = (long long)blockIdx.x * kProjRows;
     const int nr = (int)min((long long)kProjRows, rows - r0);
-    for (int i = threadIdx.x; i < kProjRows * d_in; i += kProjThreads) {
-        const int rr = i / d_in, j = i - rr * d_in;
-        s_x[i] = rr < nr ? to_f32(x[((r0 + rr) * heads + h) * d_in + j]) : 0.f;
-    }
+    proj_stage_x(s_x, x, r0, nr, heads, h, d_in);
     __syncthreads();
     const int c = blockIdx.y * kProjThreads + threadIdx.x;
     if (c >= d_out) return;
@@ -221,52 +257,48 @@ mla_absorb_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restric
 #pragma unroll
     for (int rr = 0; rr < kProjRows; ++rr) acc[rr] = 0.f;
     const T* wp = w + (long long)h * d_in * d_out + c;
-    for (int j = 0; j < d_in; ++j) {
-        const float wv = to_f32(wp[(long long)j * d_out]);
+#pragma unroll 4
+    for (int j = 0; j < d_in; ++j) proj_fma_rows(acc, s_x + j * kProjRows, to_f32(wp[(long long)j * d_out]));
 #pragma unroll
-        for (int rr = 0; rr < kProjRows; ++rr) acc[rr] += s_x[rr * d_in + j] * wv;
-    }
-    for (int rr = 0; rr < nr; ++rr) out[((r0 + rr) * heads + h) * d_out + c] = from_f32<T>(acc[rr]);
+    for (int rr = 0; rr < kProjRows; ++rr)
+        if (rr < nr) out[((r0 + rr) * heads + h) * d_out + c] = from_f32<T>(acc[rr]);
 }
 
-// out[r, h, v] = sum_c x[r, h, c] * w[h, v, c]: one warp per output column,
-// lanes stride the contraction so the weight row is read coalesced.
+// out[r, h, v] = sum_c x[r, h, c] * w[h, v, c]: one thread per output column v; it walks its
+// weight row with 16-byte loads (the other half of each 32-byte sector is the same thread's
+// next load) and reads x as shared-memory broadcasts.  No reductions across threads.
 template <typename T>
 __global__ void __launch_bounds__(kProjThreads)
 mla_value_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ out,
                  long long rows, int heads, int d_in, int d_out) {
-    extern __shared__ __align__(16) float s_x[];      // [kProjRows][d_in]
+    extern __shared__ __align__(16) float s_x[];      // [d_in][kProjRows]
     pdl_launch_dependents();
     pdl_wait();
-    constexpr int NW = kProjThreads / 32;
-    const int h = blockIdx.z, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int VEC = 16 / (int)sizeof(T);          // elements per 16-byte load
+    const int h = blockIdx.z;
     const long long r0 = (long long)blockIdx.x * kProjRows;
     const int nr = (int)min((long long)kProjRows, rows - r0);
-    for (int i = threadIdx.x; i < kProjRows * d_in; i += kProjThreads) {
-        const int rr = i / d_in, j = i - rr * d_in;
-        s_x[i] = rr < nr ? to_f32(x[((r0 + rr) * heads + h) * d_in + j]) : 0.f;
-    }
+    proj_stage_x(s_x, x, r0, nr, heads, h, d_in);
     __syncthreads();
-    constexpr int COLS = 8;                           // output columns per warp
-    const int v0 = (blockIdx.y * NW + warp) * COLS;
-    for (int v = v0; v < min(v0 + COLS, d_out); ++v) {
-        float acc[kProjRows];
+    const int v = blockIdx.y * kProjThreads + threadIdx.x;
+    if (v >= d_out) return;
+    float acc[kProjRows];
 #pragma unroll
-        for (int rr = 0; rr < kProjRows; ++rr) acc[rr] = 0.f;
-        const T* wp = w + ((long long)h * d_out + v) * d_in;
-        for (int j = lane; j < d_in; j += 32) {
-            const float wv = to_f32(wp[j]);
+    for (int rr = 0; rr < kProjRows; ++rr) acc[rr] = 0.f;
+    const T* wp = w + ((long long)h * d_out + v) * d_in;
+    int c = 0;
+    if ((d_in % VEC) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+        for (; c < d_in; c += VEC) {
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(wp + c));
+            const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-            for (int rr = 0; rr < kProjRows; ++rr) acc[rr] += s_x[rr * d_in + j] * wv;
-        }
-#pragma unroll
-        for (int rr = 0; rr < kProjRows; ++rr) {
-            float a = acc[rr];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-            if (lane == 0 && rr < nr) out[((r0 + rr) * heads + h) * d_out + v] = from_f32<T>(a);
+            for (int i = 0; i < VEC; ++i) proj_fma_rows(acc, s_x + (c + i) * kProjRows, to_f32(e[i]));
         }
     }
+    for (; c < d_in; ++c) proj_fma_rows(acc, s_x + c * kProjRows, to_f32(wp[c]));
+#pragma unroll
+    for (int rr = 0; rr < kProjRows; ++rr)
+        if (rr < nr) out[((r0 + rr) * heads + h) * d_out + v] = from_f32<T>(acc[rr]);
 }
 
 // Row slots[i] of the cache (viewed as [rows, dc + dr]) = latent[i] ++ rope[i].

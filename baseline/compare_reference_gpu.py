@@ -12,7 +12,7 @@ installed untouched into ``baseline/_ref`` with
 Both run on the same seeded synthetic workloads as ``bench.py``; outputs are
 compared with this library's before timing.  Usage:
 
-    python baseline/compare_reference_gpu.py [workload ...]
+    python baseline/compare_reference_gpu.py [workload ... | prefill | mla]
 """
 
 from __future__ import annotations
@@ -97,7 +97,41 @@ def compare_prefill(ref):
         print(json.dumps(row), flush=True)
 
 
+def compare_mla(ref):
+    """Paged latent (MLA) decode: this library vs the reference's fused CUDA operator
+    (attention/mla.py:43-53) on the synthetic MLA workloads."""
+    for name in ("m2_deepseek_h128_bf16", "m3_deepseek_h16_bf16"):
+        w = synth.MLA_WORKLOADS[name]
+        c = synth.make_mla_case(w, seed=42, device="cuda", cache_on_device=True)
+        nbytes = synth.mla_algorithmic_bytes(c["lengths"].cpu(), w)
+        args = (c["q_nope"], c["q_rope"], c["cache"], c["block_table"], c["lengths"], c["positions"],
+                c["w_uk"], c["w_uv"])
+        mine = ours.mla_decode(*args)
+        row = {"workload": name, "algorithmic_MB": round(nbytes / 1e6, 1)}
+        legs = {"b200_mla_decode": lambda: ours.mla_decode(*args),
+                "ref_cuda_mla_decode": lambda: ref.mla_decode(*args)}
+        for leg, fn in legs.items():
+            try:
+                out = fn()
+                torch.cuda.synchronize()
+                err = (out.float() - mine.float()).abs().max().item()
+                close = torch.allclose(out.float(), mine.float(), atol=2e-2, rtol=2e-2)
+                us = time_call(fn, reps=10 if leg.startswith("b200") else 1, min_seconds=0.05)
+                row[leg] = {"us": round(us, 1), "GBps": round(nbytes / us / 1e3, 1),
+                            "max_abs_diff_vs_b200": err, "close": bool(close)}
+            except Exception as exc:   # noqa: BLE001
+                row[leg] = {"error": str(exc)[:200]}
+        print(json.dumps(row), flush=True)
+
+
 def main():
+    if "mla" in sys.argv[1:]:
+        ref, why = load_reference()
+        if ref is None:
+            print(json.dumps({"unavailable": why}))
+            return
+        compare_mla(ref)
+        return
     names = [a for a in sys.argv[1:] if a != "prefill"] or (
         [] if "prefill" in sys.argv[1:] else list(synth.WORKLOADS))
     ref, why = load_reference()
