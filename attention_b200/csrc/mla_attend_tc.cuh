@@ -9,43 +9,42 @@
 //   rank 1 : latent columns 256..511 + the 64 rotated   (5 blocks)
 // Each CTA loads only its own blocks of every cache row (so every byte is read once by the
 // pair), and those same blocks serve both contractions:
-//   S_r[128 x 32]  = Q_r[128 x 64 nb] . C_r[32 x 64 nb]^T     partial scores over its columns
-//   O_r[128 x 256] += P[128 x 32] . C_r[32 x 256]             its half of the latent output
+//   S_r[128 x 64]  = Q_r[128 x 64 nb] . C_r[64 x 64 nb]^T     partial scores over its columns
+//   O_r[128 x 256] += P[128 x 64] . C_r[64 x 256]             its half of the latent output
 // The full scores are S_0 + S_1: every thread sends its partial scores to the peer CTA through
 // distributed shared memory (st.async, completing a transaction barrier there) and adds what it
 // receives, so both CTAs hold the same scores bit for bit (a + b == b + a) and take the same
-// softmax decisions without further talk.
+// softmax decisions without further talk.  (A thread only needs the peer's partials for its
+// own 32 columns; the two threads of a row swap their half-row maxima.)
 //
-// Both A operands live in tensor memory, not in shared memory: Q_r is written there once per
-// work item (tcgen05.st from registers), and P is written over the score buffer it was
-// computed from.  An MMA with 128 rows of A in shared memory re-reads 4 KB of A for every 32
-// tokens of B; that made the first version of this kernel shared-memory-bandwidth bound at
-// about a fifth of the HBM rate.  With A in TMEM an MMA reads only its B tile (the cache rows)
-// from shared memory, and shared memory holds nothing but cache tiles and the landing buffers.
+// Both A operands live in tensor memory, not in shared memory: the latent part of Q_r is
+// written there once per work item (tcgen05.st from registers), and P is written over the score
+// buffer it was computed from.  An MMA with 128 rows of A in shared memory re-reads 4 KB of A
+// for every tile of B; that made the first version of this kernel shared-memory-bandwidth
+// bound.  With A in TMEM an MMA reads only its B tile (the cache rows) from shared memory.  An
+// MMA also costs its issuing lane about 70 cycles whatever its width, and every tile costs the
+// softmax warps a fixed round of waits, TMEM round trips and fences: hence 64-token tiles.
 //
-// An MMA costs its issuing lane about 70 cycles whatever its width, so the scores of two
-// 32-token tiles are computed by one set of 64-wide MMAs (the ring keeps consecutive tiles
-// adjacent); everything else works per 32-token tile.
-//
-// TMEM (512 columns): four score buffers of 32 columns (P(j) overwrites the first 16 columns
-// of S(j)), 256 columns of output, 128 columns for the latent part of Q_r.  Shared memory: an
-// eight-stage ring of 32-token tiles (20 KB each), the rotated block of Q_r (16 KB, rank 1) and
-// two 16 KB landing buffers: 208 KB, one CTA per SM.
+// TMEM (512 columns): two score buffers of 64 columns (P(j) overwrites the first 32 columns of
+// S(j)), 256 columns of output, 128 columns for the latent part of Q_r.  Shared memory: a
+// three-stage ring of 64-token tiles (40 KB each), the rotated block of Q_r (16 KB, rank 1) and
+// two 32 KB landing buffers: 200 KB, one CTA per SM.
 //
 // Warp roles (352 threads):
-//   warps 0-7    softmax: two threads per query row (16 score columns each)
+//   warps 0-7    softmax: two threads per query row (32 score columns each)
 //   warps 8-9    loaders: 16-byte cp.async of this CTA's blocks of each cache row, one page lookup
-//                per tile when the page size is a multiple of 32 tokens, else one per row
+//                per 32 tokens when the page size is a multiple of 32 tokens, else one per row
 //   warp 10      one lane issues every tcgen05.mma
-// There is no CTA-wide barrier in the token loop; the hand-offs are mbarriers.  Every wait is
+// There is no CTA-wide barrier in the token loop; the hand-offs are mbarriers (and one 64-thread
+// named barrier between the two warps that share a TMEM lane quadrant).  Every mbarrier wait is
 // time-bounded: a wait that runs out marks the CTA dead and raises the status word, and the CTA
 // still walks the protocol to the end, so its peer is never left waiting and no CTA exits
 // while the other may still write into its memory.
-//   full[8]    64 loader arrivals (when their copies land)   tile is in its stage   -> MMA lane
-//   empty[8]   tcgen05.commit   P.C of the stage's tile is done: stage and O are free
-//   bar_s[4]   tcgen05.commit   partial scores of a tile are in TMEM                -> softmax
+//   full[3]    64 loader arrivals (when their copies land)   tile is in its stage   -> MMA lane
+//   empty[3]   tcgen05.commit   P.C of the stage's tile is done: stage and O are free
+//   bar_s[2]   tcgen05.commit   partial scores of a tile are in TMEM                -> softmax
 //   bar_p      8 warp arrivals  P is in TMEM, O rescaled                            -> MMA lane
-//   bar_x[2]   transaction barriers: the peer's st.async stores complete 16 KB per tile
+//   bar_x[2]   transaction barriers: the peer's st.async stores complete 32 KB per tile
 //   bar_free[2] 8 remote warp arrivals   the peer has consumed a landing buffer of its own
 #pragma once
 
@@ -59,12 +58,12 @@
 namespace gqa_b200 {
 
 constexpr int kMlaTcRows = 128;        // query rows (token x head) per CTA pair
-constexpr int kMlaTcBN = 32;           // tokens per tile
+constexpr int kMlaTcBN = 64;           // tokens per tile
 constexpr int kMlaTcSoftmaxThreads = 256;
 constexpr int kMlaTcLoadThreads = 64;
 constexpr int kMlaTcThreads = kMlaTcSoftmaxThreads + kMlaTcLoadThreads + 32;
-constexpr int kMlaTcStages = 8;
-constexpr int kMlaTcSBufs = 4;           // two pairs of score buffers
+constexpr int kMlaTcStages = 3;
+constexpr int kMlaTcSBufs = 2;
 constexpr int kMlaTcTmemCols = 512;
 constexpr int kMlaTcDc = 512;
 constexpr int kMlaTcDr = 64;
@@ -72,22 +71,19 @@ constexpr int kMlaTcWidth = kMlaTcDc + kMlaTcDr;
 
 struct MlaTcGeom {
     static constexpr int kBlocks = 5;                                   // 128-byte column blocks (rank 1)
-    static constexpr int kTileBlockBytes = kMlaTcBN * 128;              // 4 KB: one tile's rows of one block
-    // the ring is laid out [block][stage][32 rows][128 B], so that two consecutive tiles are 64
-    // consecutive rows of every block and one MMA can take both as its B operand
-    static constexpr int kBlockRegion = kMlaTcStages * kTileBlockBytes; // 32 KB
+    static constexpr int kTileBlockBytes = kMlaTcBN * 128;              // 8 KB: one tile's rows of one block
+    static constexpr int kStageBytes = kBlocks * kTileBlockBytes;       // 40 KB: [block][64 rows][128 B]
     static constexpr int kQRopeBytes = kMlaTcRows * 128;                // 16 KB: rotated query block (rank 1)
-    static constexpr int kXBytes = kMlaTcRows * kMlaTcBN * 4;           // 16 KB, two of them
+    static constexpr int kXBytes = kMlaTcRows * kMlaTcBN * 4;           // 32 KB, two of them
     static constexpr int kOffK = 0;
-    static constexpr int kOffQr = kOffK + kBlocks * kBlockRegion;
+    static constexpr int kOffQr = kOffK + kMlaTcStages * kStageBytes;
     static constexpr int kOffX = kOffQr + kQRopeBytes;
-    static constexpr int kSmemBytes = kOffX + 2 * kXBytes;              // 212992
+    static constexpr int kSmemBytes = kOffX + 2 * kXBytes;              // 204800
     // tensor memory columns
-    static constexpr int kColS = 0;                                     // kMlaTcSBufs x 32
+    static constexpr int kColS = 0;                                     // kMlaTcSBufs x 64
     static constexpr int kColO = kMlaTcSBufs * kMlaTcBN;                // 256
     static constexpr int kColQ = kColO + 256;                           // 128: the latent part of Q_r
     static_assert(kColQ + 4 * 32 <= kMlaTcTmemCols, "TMEM budget");
-    static_assert(kMlaTcStages % 2 == 0 && kMlaTcSBufs % 2 == 0, "tiles are issued in pairs");
 };
 
 namespace tc {
@@ -196,6 +192,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     __shared__ __align__(8) uint64_t s_bar[2 * NS + NSB + 6];
     __shared__ uint32_t s_tmem;
     __shared__ int s_dead;
+    __shared__ float s_max[2][2][kMlaTcRows];        // [tile parity][column half][row]: half-row maxima
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool is_softmax = tid < NT, is_loader = tid >= NT && tid < NT + NL, is_mma = tid >= NT + NL;
@@ -297,54 +294,59 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
                 cp_async16<0>(sqr + row * 128 + ((c ^ (row & 7)) << 4), src, valid ? 16 : 0, 0);
             }
         }
-        // this thread's chunks of a tile: the same (row, 16-byte column) for every tile
-        constexpr int MAXC = BN * 40 / NL;           // 20 chunks per thread for rank 1, 16 for rank 0
-        const int nchunk = BN * cpr / NL;
+        // this thread's chunks of a 32-row half tile: the same (row, 16-byte column) for every
+        // half (the second half of a tile is 32 rows further in both the cache page and the stage)
+        constexpr int HR = 32;                       // rows per half
+        constexpr int MAXC = HR * 40 / NL;           // 20 chunks per thread for rank 1, 16 for rank 0
+        const int nchunk = HR * cpr / NL;
         uint32_t soff[MAXC], doff[MAXC];             // byte offsets in the cache page run / in the stage
 #pragma unroll
         for (int k = 0; k < MAXC; ++k) {
             const int i = lt + k * NL;
             const int row = i / cpr, c = i - row * cpr;
             soff[k] = (uint32_t)(row * kMlaTcWidth + col0 + c * 8) * 2u;
-            doff[k] = (uint32_t)((c >> 3) * G::kBlockRegion + row * 128 + (((c & 7) ^ (row & 7)) << 4));
+            doff[k] = (uint32_t)((c >> 3) * G::kTileBlockBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4));
         }
         const char* cache = reinterpret_cast<const char*>(p.cache);
         const int32_t* trow = p.table + (long long)b * p.max_pages;
         const int last_block = (int)(p.num_blocks - 1);
-        const bool page_run = p.page_shift >= 5;     // a 32-token tile never straddles a page
+        const bool page_run = p.page_shift >= 5;     // a 32-token half never straddles a page
         for (int j = 0; j < n_tiles; ++j) {
             const int stage = j % NS;
             if (j >= NS) wait_bar(bar_empty + stage * 8, ((j / NS) - 1) & 1);
-            const uint32_t st = sk + stage * G::kTileBlockBytes;
-            const int tok0 = t0 + j * BN;
-            if (page_run) {
-                const int pg = tok0 >> p.page_shift;
-                // a page id outside the pool (a caller error) is clamped instead of faulting
-                const long long phys = min(max(__ldg(trow + pg), 0), last_block);
-                const char* base = cache + (phys * p.page + (tok0 & (p.page - 1))) * (kMlaTcWidth * 2);
-                const int rows_ok = t1 - tok0;       // rows below this are inside the chunk
 #pragma unroll
-                for (int k = 0; k < MAXC; ++k) {
-                    if (k < nchunk) {
-                        const bool valid = (int)((doff[k] >> 7) & 31u) < rows_ok;
-                        cp_async16<0>(st + doff[k], valid ? base + soff[k] : cache, valid ? 16 : 0, 0);
-                    }
-                }
-            } else {
+            for (int half = 0; half < BN / HR; ++half) {
+                const uint32_t st = sk + stage * G::kStageBytes + half * (HR * 128);
+                const int tok0 = t0 + j * BN + half * HR;
+                if (page_run) {
+                    const int pg = min(tok0 >> p.page_shift, p.max_pages - 1);
+                    // a page id outside the pool (a caller error) is clamped instead of faulting
+                    const long long phys = min(max(__ldg(trow + pg), 0), last_block);
+                    const char* base = cache + (phys * p.page + (tok0 & (p.page - 1))) * (kMlaTcWidth * 2);
+                    const int rows_ok = t1 - tok0;   // rows below this are inside the chunk
 #pragma unroll
-                for (int k = 0; k < MAXC; ++k) {
-                    if (k < nchunk) {
-                        const int row = (int)((doff[k] >> 7) & 31u);
-                        const int tok = tok0 + row;
-                        const bool valid = tok < t1;
-                        const char* src = cache;
-                        if (valid) {
-                            const int pg = p.page_shift >= 0 ? tok >> p.page_shift : tok / p.page;
-                            const long long phys = min(max(__ldg(trow + pg), 0), last_block);
-                            src = cache + (phys * p.page + (tok - pg * p.page)) * (kMlaTcWidth * 2) +
-                                  (soff[k] - (uint32_t)row * (kMlaTcWidth * 2));
+                    for (int k = 0; k < MAXC; ++k) {
+                        if (k < nchunk) {
+                            const bool valid = (int)((doff[k] >> 7) & 31u) < rows_ok;
+                            cp_async16<0>(st + doff[k], valid ? base + soff[k] : cache, valid ? 16 : 0, 0);
                         }
-                        cp_async16<0>(st + doff[k], src, valid ? 16 : 0, 0);
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < MAXC; ++k) {
+                        if (k < nchunk) {
+                            const int row = (int)((doff[k] >> 7) & 31u);
+                            const int tok = tok0 + row;
+                            const bool valid = tok < t1;
+                            const char* src = cache;
+                            if (valid) {
+                                const int pg = p.page_shift >= 0 ? tok >> p.page_shift : tok / p.page;
+                                const long long phys = min(max(__ldg(trow + pg), 0), last_block);
+                                src = cache + (phys * p.page + (tok - pg * p.page)) * (kMlaTcWidth * 2) +
+                                      (soff[k] - (uint32_t)row * (kMlaTcWidth * 2));
+                            }
+                            cp_async16<0>(st + doff[k], src, valid ? 16 : 0, 0);
+                        }
                     }
                 }
             }
@@ -354,75 +356,64 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     } else if (is_mma) {
         // =============================== MMA warp: one lane issues everything ===============================
         if (lane == 0) {
-            const uint32_t idesc_s1 = tc::idesc_f16(BM, BN, AB_TYPE);        // one tile
-            const uint32_t idesc_s2 = tc::idesc_f16(BM, 2 * BN, AB_TYPE);    // a pair of tiles
+            const uint32_t idesc_s = tc::idesc_f16(BM, BN, AB_TYPE);
             const uint32_t idesc_o = tc::idesc_f16(BM, 256, AB_TYPE) | tc::kIdescBMnMajor;
             // Descriptors differ only in their start-address field ((address >> 4) in the low bits,
             // no carry out of it below 256 KB), so each one is a base plus a small offset: the
             // issuing lane's instruction stream per MMA stays a handful of instructions.
             const uint64_t dk0 = tc::smem_desc_sw128_kmajor(sk);
             const uint64_t dqr0 = tc::smem_desc_sw128_kmajor(sqr);
-            const uint64_t dv0 = tc::smem_desc_sw128_mnmajor(sk, G::kBlockRegion);
-            // Partial scores of tiles j and j+1 (or of tile j alone) in one set of MMAs: an MMA costs
-            // the issuing lane about 70 cycles whatever its width, so the pair halves that cost per
-            // token.  j is even, so the two stages and the two score buffers are adjacent.  A = the
-            // latent part of Q_r from tensor memory (8 columns = 16 elements per step) and, on
-            // rank 1, its rotated block from shared memory.
-            auto issue_qk = [&](int j, bool pair) {
-                const uint64_t dk = dk0 + (uint64_t)(((j % NS) * G::kTileBlockBytes) >> 4);
+            const uint64_t dv0 = tc::smem_desc_sw128_mnmajor(sk, G::kTileBlockBytes);
+            // S_r(j) = Q_r C_r(j)^T into score buffer j & 1.  A = the latent part of Q_r from tensor
+            // memory (8 columns = 16 elements per step) and, on rank 1, its rotated block from
+            // shared memory.  (An MMA costs the issuing lane about 70 cycles whatever its width,
+            // which is why the tile is 64 tokens wide and not 32.)
+            auto issue_qk = [&](int j) {
+                const uint64_t dk = dk0 + (uint64_t)(((j % NS) * G::kStageBytes) >> 4);
                 const uint32_t d = tmem + (j % NSB) * BN;
-                const uint32_t idesc = pair ? idesc_s2 : idesc_s1;
 #pragma unroll
                 for (int blk = 0; blk < 4; ++blk) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         tc::mma_f16_ts(d, tmem_q + blk * 32 + k * 8,
-                                       dk + (uint64_t)((blk * G::kBlockRegion + k * 32) >> 4), idesc, (blk | k) ? 1u : 0u);
+                                       dk + (uint64_t)((blk * G::kTileBlockBytes + k * 32) >> 4), idesc_s,
+                                       (blk | k) ? 1u : 0u);
                 }
                 if (rank) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         tc::mma_f16_ss(d, dqr0 + (uint64_t)((k * 32) >> 4),
-                                       dk + (uint64_t)((4 * G::kBlockRegion + k * 32) >> 4), idesc, 1u);
+                                       dk + (uint64_t)((4 * G::kTileBlockBytes + k * 32) >> 4), idesc_s, 1u);
                 }
                 tc::mma_commit(bar_s0 + (j % NSB) * 8);
-                if (pair) tc::mma_commit(bar_s0 + ((j + 1) % NSB) * 8);
             };
-            // O_r += P C_r(j): A = P(j) from the first 16 columns of score buffer j % NSB, B = the first
+            // O_r += P C_r(j): A = P(j) from the first 32 columns of score buffer j & 1, B = the first
             // four blocks of the stage as an MN-major operand
             auto issue_pv = [&](int j) {
-                const uint64_t dv = dv0 + (uint64_t)(((j % NS) * G::kTileBlockBytes) >> 4);
+                const uint64_t dv = dv0 + (uint64_t)(((j % NS) * G::kStageBytes) >> 4);
                 const uint32_t pa = tmem + (j % NSB) * BN;
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k)
                     tc::mma_f16_ts(tmem_o, pa + k * 8, dv + (uint64_t)((k * 2048) >> 4), idesc_o, (j | k) ? 1u : 0u);
                 tc::mma_commit(bar_empty + (j % NS) * 8);
             };
-            // wait for the tiles of the pair starting at tile j to land, then issue their scores
-            auto scores_of_pair = [&](int j) {
-                const bool pair = j + 1 < n_tiles;
+            auto scores_of = [&](int j) {             // wait for tile j to land, then issue its scores
                 wait_bar(bar_full + (j % NS) * 8, (j / NS) & 1);
-                if (pair) wait_bar(bar_full + ((j + 1) % NS) * 8, ((j + 1) / NS) & 1);
                 tc::fence_async_smem();
                 tc::tc_fence_after();
-                issue_qk(j, pair);
+                issue_qk(j);
             };
             wait_bar(bar_q, 0);                      // Q_r is in tensor memory
             tc::tc_fence_after();
-            scores_of_pair(0);                       // (the rotated block of Q_r rides on full[0])
-            if (n_tiles > 2) scores_of_pair(2);
-            for (int j = 0; j < n_tiles; j += 2) {
+            scores_of(0);                            // (the rotated block of Q_r rides on full[0])
+            if (n_tiles > 1) scores_of(1);
+            for (int j = 0; j < n_tiles; ++j) {
                 wait_bar(bar_p, j & 1);              // P(j) is in tensor memory, O rescaled
                 tc::tc_fence_after();
                 issue_pv(j);
-                if (j + 1 < n_tiles) {
-                    wait_bar(bar_p, (j + 1) & 1);
-                    tc::tc_fence_after();
-                    issue_pv(j + 1);
-                }
-                // the pair after next reuses this pair's score buffers: P.C(j), P.C(j+1) are queued
-                // ahead of it and the tensor pipe runs in order
-                if (j + 4 < n_tiles) scores_of_pair(j + 4);
+                // S(j+2) reuses the buffer of S(j) / P(j): P.C(j) is queued ahead of it and the tensor
+                // pipe runs in order
+                if (j + 2 < n_tiles) scores_of(j + 2);
             }
         }
         __syncwarp();
@@ -462,64 +453,76 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             if (lane == 0) tc::mbar_arrive(bar_q);
         }
 
-        // partial scores of tile t: TMEM -> registers -> this thread's 16 columns into landing
+        // this thread's 32 columns of the partial scores of tile t: TMEM -> registers -> landing
         // buffer t & 1 of the peer (once the peer has consumed tile t - 2 from it)
-        auto fetch_and_send = [&](int t, uint32_t (&r)[32]) {
+        auto send_partial = [&](int t) {
             wait_bar(bar_s0 + (t % NSB) * 8, (t / NSB) & 1);
             tc::tc_fence_after();
-            tc::tmem_ld32(tmem + (t % NSB) * BN + lane_sel, r);
+            uint32_t r[32];
+            tc::tmem_ld32(tmem + (t % NSB) * BN + lane_sel + hf * HC, r);
             tc::tmem_ld_wait();
-            if (t >= 2) wait_bar_cluster(bar_free + (t & 1) * 8, ((t >> 1) - 1) & 1);
-            const uint32_t dst = peer_sx + (t & 1) * G::kXBytes + row_l * 16, dbar = peer_bar_x + (t & 1) * 8;
-            if (hf == 0) {                           // warp-uniform: static register indices, no selects
+            // (no data is read after this wait, so it needs no cluster-scope acquire)
+            if (t >= 2) wait_bar(bar_free + (t & 1) * 8, ((t >> 1) - 1) & 1);
+            const uint32_t dst = peer_sx + (t & 1) * G::kXBytes + (hf * (HC / 4) * BM + row_l) * 16;
+            const uint32_t dbar = peer_bar_x + (t & 1) * 8;
 #pragma unroll
-                for (int q4 = 0; q4 < HC / 4; ++q4)
-                    tc::st_async_v4(dst + q4 * (BM * 16), r[q4 * 4], r[q4 * 4 + 1], r[q4 * 4 + 2], r[q4 * 4 + 3], dbar);
-            } else {
-#pragma unroll
-                for (int q4 = HC / 4; q4 < HC / 2; ++q4)
-                    tc::st_async_v4(dst + q4 * (BM * 16), r[q4 * 4], r[q4 * 4 + 1], r[q4 * 4 + 2], r[q4 * 4 + 3], dbar);
-            }
+            for (int q4 = 0; q4 < HC / 4; ++q4)
+                tc::st_async_v4(dst + q4 * (BM * 16), r[q4 * 4], r[q4 * 4 + 1], r[q4 * 4 + 2], r[q4 * 4 + 3], dbar);
         };
-        // one tile of the softmax; r holds this tile's partial scores, rn receives the next tile's
-        auto softmax_tile = [&](int j, uint32_t (&r)[32], uint32_t (&rn)[32]) {
-            // ---- the next tile's partial scores travel while this tile is processed ----
-            if (j + 1 < n_tiles) fetch_and_send(j + 1, rn);
-
-            // ---- full scores = mine + the peer's ----
-            wait_bar(bar_x + (j & 1) * 8, (j >> 1) & 1);
-            // announce the bytes of tile j + 2 on the same barrier; they cannot land before every
-            // warp here has passed the wait above, because the peer sends them only after all
-            // warps have released the buffer below
-            if (tid == 0 && j + 2 < n_tiles) tc::mbar_arrive_expect_tx(bar_x + (j & 1) * 8, G::kXBytes);
-            float s[BN];
+        // full scores of 32 columns starting at column c0 of tile j: partial (TMEM) + the peer's
+        auto full_scores = [&](int j, int c0, float (&s)[32]) {
+            uint32_t r[32];
+            tc::tmem_ld32(tmem + (j % NSB) * BN + lane_sel + c0, r);
+            tc::tmem_ld_wait();
+            const uint32_t xb = sx + (j & 1) * G::kXBytes + ((c0 / 4) * BM + row_l) * 16;
 #pragma unroll
-            for (int c4 = 0; c4 < BN / 4; ++c4) {
+            for (int c4 = 0; c4 < 8; ++c4) {
                 uint32_t x0, x1, x2, x3;
                 asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3)
-                             : "r"(sx + (j & 1) * G::kXBytes + (c4 * BM + row_l) * 16) : "memory");
+                             : "r"(xb + c4 * (BM * 16)) : "memory");
                 s[c4 * 4 + 0] = __uint_as_float(r[c4 * 4 + 0]); s[c4 * 4 + 1] = __uint_as_float(r[c4 * 4 + 1]);
                 s[c4 * 4 + 2] = __uint_as_float(r[c4 * 4 + 2]); s[c4 * 4 + 3] = __uint_as_float(r[c4 * 4 + 3]);
                 tc::add2(s[c4 * 4 + 0], s[c4 * 4 + 1], __uint_as_float(x0), __uint_as_float(x1));
                 tc::add2(s[c4 * 4 + 2], s[c4 * 4 + 3], __uint_as_float(x2), __uint_as_float(x3));
             }
-            __syncwarp();
-            if (lane == 0) tc::mbar_arrive_remote_relaxed(peer_bar_free + (j & 1) * 8);   // buffer released
-            const int tok0 = t0 + j * BN;
-            if (tok0 + BN > my_stop) {
+            const int tok0 = t0 + j * BN + c0;
+            if (tok0 + 32 > my_stop) {
 #pragma unroll
-                for (int c = 0; c < BN; ++c)
+                for (int c = 0; c < 32; ++c)
                     if (tok0 + c >= my_stop) s[c] = -INFINITY;
             }
+        };
+        auto max_of = [&](const float (&s)[32]) {
             float a0 = s[0], a1 = s[1], a2 = s[2], a3 = s[3];
 #pragma unroll
-            for (int c = 4; c < BN - 4; c += 8) {
+            for (int c = 4; c < 28; c += 8) {
                 a0 = tc::max3(a0, s[c], s[c + 1]); a1 = tc::max3(a1, s[c + 2], s[c + 3]);
                 a2 = tc::max3(a2, s[c + 4], s[c + 5]); a3 = tc::max3(a3, s[c + 6], s[c + 7]);
             }
-            a0 = tc::max3(a0, s[BN - 4], s[BN - 3]);
-            a1 = tc::max3(a1, s[BN - 2], s[BN - 1]);
-            const float mx = fmaxf(tc::max3(a0, a1, a2), a3) * p.scale_log2;
+            a0 = tc::max3(a0, s[28], s[29]);
+            a1 = tc::max3(a1, s[30], s[31]);
+            return fmaxf(tc::max3(a0, a1, a2), a3);
+        };
+
+        send_partial(0);
+        for (int j = 0; j < n_tiles; ++j) {
+            // ---- full scores = mine + the peer's; the other half of the row only for the maximum ----
+            wait_bar(bar_x + (j & 1) * 8, (j >> 1) & 1);
+            // announce the bytes of tile j + 2 on the same barrier; they cannot land before every
+            // warp here has passed the wait above, because the peer sends them only after all
+            // warps have released the buffer below
+            if (tid == 0 && j + 2 < n_tiles) tc::mbar_arrive_expect_tx(bar_x + (j & 1) * 8, G::kXBytes);
+            // this thread's half of the row; the two threads of a row swap their maxima through
+            // shared memory when the two warps of the lane quadrant meet.  After that meeting both
+            // have read S(j) and the landing buffer: the buffer goes back to the peer, and P(j) may
+            // overwrite S(j).
+            float s[32];
+            full_scores(j, hf * HC, s);
+            float mx = max_of(s);
+            s_max[j & 1][hf][row_l] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
+            mx = fmaxf(mx, s_max[j & 1][hf ^ 1][row_l]) * p.scale_log2;
+            if (lane == 0) tc::mbar_arrive_remote_relaxed(peer_bar_free + (j & 1) * 8);
             const bool need = mx > m_run + kRescaleSlack;
             float alpha = 1.f;
             if (need) {
@@ -528,28 +531,20 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
                 m_run = mn;
                 l_run *= alpha;
             }
-            const float ref = m_run == -INFINITY ? 0.f : m_run;
+            const float nref = m_run == -INFINITY ? 0.f : -m_run;
             uint32_t pw[HC / 2];
             {
-                const float nref = -ref;
-                float e[HC];                         // this thread's half of the row, as exponents
-                if (hf == 0) {                       // warp-uniform: static register indices
-#pragma unroll
-                    for (int c = 0; c < HC; c += 2) tc::fma2(e[c], e[c + 1], s[c], s[c + 1], p.scale_log2, nref);
-                } else {
-#pragma unroll
-                    for (int c = 0; c < HC; c += 2) tc::fma2(e[c], e[c + 1], s[HC + c], s[HC + c + 1], p.scale_log2, nref);
-                }
                 float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
                 for (int c = 0; c < HC; c += 2) {
-                    const float p0 = fast_exp2(e[c]), p1 = fast_exp2(e[c + 1]);
+                    float e0, e1;
+                    tc::fma2(e0, e1, s[c], s[c + 1], p.scale_log2, nref);
+                    const float p0 = fast_exp2(e0), p1 = fast_exp2(e1);
                     tc::add2(ps0, ps1, p0, p1);
                     pw[c / 2] = Ops::pack(p0, p1);
                 }
                 l_run += ps0 + ps1;                  // this thread's half of the row sum
             }
-
             // ---- O may be rescaled once P.C(j-1) is done ----
             if (j > 0 && __any_sync(0xffffffffu, need)) {   // warp-uniform: TMEM ld/st are collective
                 wait_bar(bar_empty + ((j - 1) % NS) * 8, ((j - 1) / NS) & 1);
@@ -564,20 +559,14 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
                     tc::tmem_st32(tmem_o + lane_sel + c0, o);
                 }
             }
-            // ---- P(j) goes over the first 16 columns of S(j): every warp has read S(j) once the
-            //      previous tile's P is complete (a warp fetches S(j) before it arrives for tile j-1) ----
-            if (j > 0) wait_bar(bar_p, (j - 1) & 1);
-            tc::tmem_st8(tmem + (j % NSB) * BN + lane_sel + hf * (HC / 2), pw);
+            // ---- P(j) goes over the first 32 columns of S(j) ----
+            tc::tmem_st16(tmem + (j % NSB) * BN + lane_sel + hf * (HC / 2), pw);
             tc::tmem_st_wait();
             tc::tc_fence_before();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(bar_p);
-        };
-        uint32_t ra[32], rb[32];                     // ping-pong: no register copies between tiles
-        fetch_and_send(0, ra);
-        for (int j = 0; j < n_tiles; j += 2) {
-            softmax_tile(j, ra, rb);
-            if (j + 1 < n_tiles) softmax_tile(j + 1, rb, ra);
+            // ---- the next tile's partial scores travel while the tensor cores take P(j) ----
+            if (j + 1 < n_tiles) send_partial(j + 1);
         }
         wait_bar(bar_empty + ((n_tiles - 1) % NS) * 8, ((n_tiles - 1) / NS) & 1);
         tc::tc_fence_after();
