@@ -139,6 +139,9 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
+__device__ __forceinline__ void mbar_inval(uint32_t bar) {
+    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 // one non-blocking test of a barrier phase
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
     uint32_t done;
@@ -176,8 +179,98 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
 }
 }  // namespace tc
 
-// grid (2 * chunks, row tiles, batch), cluster (2, 1, 1).  p.splits = chunks per sequence
-// (partials when > 1), p.chunk_tokens = tokens per chunk, p.page_shift = log2(page) or -1.
+// Schedule of the tensor-core kernel, computed on the device from the lengths (the host never
+// reads them): tiles per unit, their exclusive prefix sum, and the number of consecutive tiles
+// each range gets so that `pairs` CTA pairs share the tiles evenly.  One CTA.
+constexpr int kMlaTcPlanThreads = 256;
+constexpr int kMlaTcMinRange = 4;       // a range is at least 4 tiles (256 tokens)
+__global__ void __launch_bounds__(kMlaTcPlanThreads)
+mla_tc_plan_kernel(const MlaParams p, int pairs) {
+    __shared__ int s_sum[kMlaTcPlanThreads];
+    const int tid = threadIdx.x, U = p.tc_units, R = p.tq * p.heads;
+    const int per = (U + kMlaTcPlanThreads - 1) / kMlaTcPlanThreads;
+    const int lo = min(U, tid * per), hi = min(U, lo + per);
+    int* prefix = p.tc_sched + 4;
+    auto tiles_of = [&](int u) {
+        const int b = u / p.tc_row_tiles, g0 = (u - b * p.tc_row_tiles) * kMlaTcRows;
+        int end_max = 0;
+        for (int t = g0 / p.heads; t <= (min(R, g0 + kMlaTcRows) - 1) / p.heads; ++t)
+            end_max = max(end_max, mla_row_end(p, b, t));
+        end_max = min(end_max, p.page * p.max_pages);    // a length past the table is clamped
+        return (end_max + kMlaTcBN - 1) / kMlaTcBN;
+    };
+    int sum = 0;
+    for (int u = lo; u < hi; ++u) sum += tiles_of(u);
+    s_sum[tid] = sum;
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int i = 0; i < kMlaTcPlanThreads; ++i) { const int x = s_sum[i]; s_sum[i] = run; run += x; }
+        const int per_range = p.tc_force_range > 0 ? p.tc_force_range
+                                                   : max(kMlaTcMinRange, (run + pairs - 1) / pairs);
+        p.tc_sched[0] = run;
+        p.tc_sched[1] = per_range;
+        p.tc_sched[2] = (run + per_range - 1) / per_range;
+        prefix[U] = run;
+    }
+    __syncthreads();
+    int run = s_sum[tid];
+    for (int u = lo; u < hi; ++u) { prefix[u] = run; run += tiles_of(u); }
+}
+
+// One warp per query row: fold the partial slots of the row's unit (slot = range + unit, for
+// the ranges that overlap the unit), or nothing when one item covered the whole unit and wrote
+// the final rows itself; rows of units without any visible token are zeroed here.
+template <typename T>
+__global__ void __launch_bounds__(kMlaMergeWarps * 32)
+mla_tc_merge_kernel(const MlaParams p) {
+    const int lane = threadIdx.x & 31;
+    const long long wid = (long long)blockIdx.x * kMlaMergeWarps + (threadIdx.x >> 5);
+    const int u = (int)(wid / kMlaTcRows), r = (int)(wid - (long long)u * kMlaTcRows);
+    if (u >= p.tc_units) return;
+    const int R = p.tq * p.heads;
+    const int b = u / p.tc_row_tiles, g = (u - b * p.tc_row_tiles) * kMlaTcRows + r;
+    if (g >= R) return;
+    const int* prefix = p.tc_sched + 4;
+    const int per_range = p.tc_sched[1];
+    const int first = prefix[u], tiles = prefix[u + 1] - first;
+    T* op = reinterpret_cast<T*>(p.out) + ((long long)b * R + g) * kMlaTcDc;
+    if (tiles == 0) {
+        for (int d = lane * 4; d < kMlaTcDc; d += 128) {
+            op[d] = from_f32<T>(0.f); op[d + 1] = from_f32<T>(0.f);
+            op[d + 2] = from_f32<T>(0.f); op[d + 3] = from_f32<T>(0.f);
+        }
+        return;
+    }
+    const int r0 = first / per_range, r1 = (first + tiles - 1) / per_range;
+    if (r0 == r1) return;                            // one item covered the unit
+    const float* ml = p.part_ml + ((long long)(r0 + u) * kMlaTcRows + r) * 2;         // slot stride below
+    const float* acc = p.part_acc + ((long long)(r0 + u) * kMlaTcRows + r) * kMlaTcDc;
+    const long long ml_stride = (long long)kMlaTcRows * 2, acc_stride = (long long)kMlaTcRows * kMlaTcDc;
+    const int n = r1 - r0 + 1;
+    float mx = -INFINITY;
+    for (int s = 0; s < n; ++s)
+        if (ml[s * ml_stride + 1] > 0.f) mx = fmaxf(mx, ml[s * ml_stride]);
+    float sum = 0.f;
+    for (int s = 0; s < n; ++s)
+        if (ml[s * ml_stride + 1] > 0.f) sum += fast_exp2(ml[s * ml_stride] - mx) * ml[s * ml_stride + 1];
+    const float inv = sum > 0.f ? 1.f / sum : 0.f;
+    for (int d = lane * 4; d < kMlaTcDc; d += 128) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < n; ++s) {
+            if (ml[s * ml_stride + 1] > 0.f) {
+                const float w = fast_exp2(ml[s * ml_stride] - mx);
+                const float4 x = *reinterpret_cast<const float4*>(acc + s * acc_stride + d);
+                a.x += w * x.x; a.y += w * x.y; a.z += w * x.z; a.w += w * x.w;
+            }
+        }
+        op[d] = from_f32<T>(a.x * inv); op[d + 1] = from_f32<T>(a.y * inv);
+        op[d + 2] = from_f32<T>(a.z * inv); op[d + 3] = from_f32<T>(a.w * inv);
+    }
+}
+
+// grid (2 * pairs), cluster (2, 1, 1): persistent pairs that walk the schedule written by
+// mla_tc_plan_kernel (p.tc_sched).  p.page_shift = log2(page) or -1.
 template <typename T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMlaTcThreads, 1)
 mla_attend_tc_kernel(const MlaParams p, int* status) {
@@ -195,39 +288,14 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     __shared__ float s_max[2][2][kMlaTcRows];        // [tile parity][column half][row]: half-row maxima
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const bool is_softmax = tid < NT, is_loader = tid >= NT && tid < NT + NL, is_mma = tid >= NT + NL;
+    const bool is_loader = tid >= NT && tid < NT + NL, is_mma = tid >= NT + NL;
     const int quad = warp & 3, hf = (warp >> 2) & 1; // softmax warps: TMEM lane quadrant, column half
     const int row_l = quad * 32 + lane;              // softmax thread's row of the 128-row tile
     const uint32_t rank = tc::cluster_ctarank(), peer = rank ^ 1u;
-    const int chunk = blockIdx.x >> 1, b = blockIdx.z;
     const int R = p.tq * p.heads;                    // query rows of one sequence
-    const int g0 = blockIdx.y * BM, g = g0 + row_l;
     const int nb = rank ? 5 : 4;                     // 128-byte blocks this CTA owns
     const int col0 = rank ? 256 : 0;                 // first cache column this CTA owns
-
-    int end_max = 0;
-    for (int t = g0 / p.heads; t <= (min(R, g0 + BM) - 1) / p.heads; ++t) end_max = max(end_max, mla_row_end(p, b, t));
-    const int t0 = chunk * p.chunk_tokens;
-    const int t1 = min(end_max, t0 + p.chunk_tokens);
-    const int n_tiles = t1 > t0 ? (t1 - t0 + BN - 1) / BN : 0;
-    const long long grow = (long long)b * R + g;     // global query row (softmax threads)
     T* op = reinterpret_cast<T*>(p.out);
-
-    if (n_tiles == 0) {                              // nothing visible in this chunk (both CTAs agree)
-        if (is_softmax && g < R) {
-            if (p.splits > 1) {
-                if (rank == 0 && hf == 0) {
-                    p.part_ml[(grow * p.splits + chunk) * 2] = -INFINITY;
-                    p.part_ml[(grow * p.splits + chunk) * 2 + 1] = 0.f;
-                }
-            } else {
-                uint4* dst = reinterpret_cast<uint4*>(op + grow * kMlaTcDc + col0 + hf * 128);
-#pragma unroll
-                for (int c = 0; c < 16; ++c) dst[c] = make_uint4(0u, 0u, 0u, 0u);
-            }
-        }
-        return;
-    }
 
     const uint32_t s_base = tc::smem_u32(smem);
     if (s_base & 1023u) {                            // the swizzled tiles need a 1024-byte aligned base
@@ -244,7 +312,57 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     const uint32_t bar_q = tc::smem_u32(&s_bar[2 * NS + NSB + 5]);
 
     if (warp == 0) { tc::tmem_alloc(tc::smem_u32(&s_tmem), kMlaTcTmemCols); tc::tmem_relinquish(); }
+    if (tid == 0) s_dead = 0;
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    const uint32_t tmem = s_tmem;
+    const uint32_t tmem_o = tmem + G::kColO, tmem_q = tmem + G::kColQ;
+
+    // ---- this pair's share of the work: ranges of `per_range` consecutive tiles of the global
+    //      tile sequence (all tiles of unit 0, then unit 1, ...; a unit = 128 query rows of one
+    //      sequence).  A range may end inside a unit and start the next one: every (range, unit)
+    //      overlap is one work item, and range + unit is a distinct partial slot for each. ----
+    const int* sched = p.tc_sched;
+    const int total_tiles = sched[0], per_range = sched[1], n_ranges = sched[2];
+    const int* prefix = sched + 4;                   // prefix[u] = tiles before unit u, [units + 1]
+    bool first_item = true;
+    for (int range = blockIdx.x >> 1; range < n_ranges; range += gridDim.x >> 1) {
+    int pos = range * per_range;
+    const int range_end = min(total_tiles, pos + per_range);
+    int u = 0;
+    {   // last unit whose first tile is at or before pos
+        int lo = 0, hi = p.tc_units;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (prefix[mid] <= pos) lo = mid; else hi = mid;
+        }
+        u = lo;
+    }
+    while (pos < range_end) {
+    while (prefix[u + 1] <= pos) ++u;                // units without tiles, or already done
+    const int u_lo = prefix[u], u_tiles = prefix[u + 1] - u_lo;
+    const int seg_lo = pos - u_lo, seg_hi = min(u_tiles, range_end - u_lo);
+    pos = u_lo + seg_hi;
+    const int slot = range + u;
+    const bool final_out = seg_lo == 0 && seg_hi == u_tiles;   // the item is the whole unit: no partial
+
+    // =============================== one work item ===============================
+    const int b = u / p.tc_row_tiles;
+    const int g0 = (u - b * p.tc_row_tiles) * BM, g = g0 + row_l;
+    int end_max = 0;
+    for (int t = g0 / p.heads; t <= (min(R, g0 + BM) - 1) / p.heads; ++t) end_max = max(end_max, mla_row_end(p, b, t));
+    end_max = min(end_max, p.page * p.max_pages);    // a length past the table is clamped (as in the plan)
+    const int t0 = seg_lo * BN;
+    const int t1 = min(end_max, seg_hi * BN);
+    const int n_tiles = seg_hi - seg_lo;
+    const long long grow = (long long)b * R + g;     // global query row (softmax threads)
+
     if (tid == 0) {
+        if (!first_item) {
+#pragma unroll
+            for (int i = 0; i < 2 * NS + NSB + 6; ++i) tc::mbar_inval(bar_full + i * 8);
+        }
 #pragma unroll
         for (int i = 0; i < NS; ++i) { tc::mbar_init(bar_full + i * 8, NL); tc::mbar_init(bar_empty + i * 8, 1); }
 #pragma unroll
@@ -259,14 +377,12 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         tc::fence_mbar_init();
         tc::mbar_arrive_expect_tx(bar_x, G::kXBytes);                          // tile 0
         if (n_tiles > 1) tc::mbar_arrive_expect_tx(bar_x + 8, G::kXBytes);     // tile 1
-        s_dead = 0;
     }
+    first_item = false;
     tc::tc_fence_before();
     __syncthreads();
     tc::cluster_sync_all();                          // both CTAs' barriers exist before any remote arrival
     tc::tc_fence_after();
-    const uint32_t tmem = s_tmem;
-    const uint32_t tmem_o = tmem + G::kColO, tmem_q = tmem + G::kColQ;
     bool alive = true;
 
     auto timed_out = [&]() {
@@ -576,9 +692,8 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         s_half[hf * BM + row_l] = l_run;
         asm volatile("bar.sync 1, %0;" ::"n"(kMlaTcSoftmaxThreads) : "memory");   // softmax warps only
         const float l_tot = l_run + s_half[(hf ^ 1) * BM + row_l];
-        const bool final_out = p.splits == 1;
         const float inv = final_out ? (l_tot > 0.f ? 1.f / l_tot : 0.f) : 1.f;
-        float* pacc = final_out ? nullptr : p.part_acc + (grow * p.splits + chunk) * kMlaTcDc + col0;
+        float* pacc = p.part_acc + ((long long)slot * BM + row_l) * kMlaTcDc + col0;
 #pragma unroll
         for (int c0 = hf * 128; c0 < (hf + 1) * 128; c0 += 32) {
             uint32_t o[32];
@@ -605,14 +720,21 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             }
         }
         if (!final_out && g < R && alive && rank == 0 && hf == 0) {
-            p.part_ml[(grow * p.splits + chunk) * 2] = m_run;
-            p.part_ml[(grow * p.splits + chunk) * 2 + 1] = l_tot;
+            p.part_ml[((long long)slot * BM + row_l) * 2] = m_run;
+            p.part_ml[((long long)slot * BM + row_l) * 2 + 1] = l_tot;
         }
     }
+    // ---- end of the item: nobody re-initialises a barrier, reuses a buffer or leaves while
+    //      the peer may still signal this CTA or write into it ----
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::cluster_sync_all();
+    tc::tc_fence_after();
+    }   // items of a range
+    }   // ranges of this pair
     tc::tc_fence_before();
     __syncthreads();
     if (warp == 0) tc::tmem_dealloc(tmem, kMlaTcTmemCols);
-    tc::cluster_sync_all();                          // neither CTA leaves while the other may still signal it
 }
 
 }  // namespace gqa_b200

@@ -59,19 +59,29 @@ cudaError_t mla_tc_status_address(int** out) {
     return cudaSuccess;
 }
 
-// Split of the tensor-core kernel: chunks of equal token count, a function of the static
-// shape only.  Starting from one chunk per sequence, the chunk is halved (not below 256
-// tokens) until there are at least two CTA pairs of work per pair of SMs.
-void tc_chunking(long long units, int capacity, int sm_pairs, int* chunk_tokens, int* splits) {
-    int chunk = (capacity + kMlaTcBN - 1) / kMlaTcBN * kMlaTcBN;
-    auto count = [&](int c) { return (capacity + c - 1) / c; };
-    while (chunk > 256 && units * count(chunk) < 2LL * sm_pairs) {
-        int half = (chunk / 2 + kMlaTcBN - 1) / kMlaTcBN * kMlaTcBN;
-        chunk = half < 256 ? 256 : half;
-    }
-    while (count(chunk) > 64) chunk *= 2;
-    *chunk_tokens = chunk;
-    *splits = count(chunk);
+// Scratch of the tensor-core kernel: the schedule (4 ints + units + 1 prefix entries), then one
+// partial slot (128 rows x (2 + 512) floats) per (range, unit) overlap; range + unit is the slot,
+// so ranges + units slots suffice.  With the automatic schedule there are at most `pairs` ranges;
+// with a forced range length, one range per `force_range` tiles of the capacity.
+struct TcScratch {
+    size_t sched_bytes, ml_bytes, acc_bytes;
+    size_t total() const { return sched_bytes + ml_bytes + acc_bytes; }
+};
+TcScratch tc_scratch(long long units, int capacity, int pairs, int force_range) {
+    const long long cap_tiles = units * ((capacity + kMlaTcBN - 1) / kMlaTcBN);
+    const long long ranges = force_range > 0 ? (cap_tiles + force_range - 1) / force_range : pairs;
+    const long long slots = ranges + units;
+    TcScratch t;
+    t.sched_bytes = align_up((size_t)(units + 5) * sizeof(int), 256);
+    t.ml_bytes = align_up((size_t)slots * kMlaTcRows * 2 * sizeof(float), 256);
+    t.acc_bytes = align_up((size_t)slots * kMlaTcRows * kMlaTcDc * sizeof(float), 256);
+    return t;
+}
+int tc_force_range(int capacity, int splits) {       // an explicit split count: that many ranges per unit
+    if (splits <= 0) return 0;
+    const int cap_tiles = (capacity + kMlaTcBN - 1) / kMlaTcBN;
+    const int fr = (cap_tiles + splits - 1) / splits;
+    return fr < 1 ? 1 : fr;
 }
 
 bool tc_eligible(int dtype, int dc, int dr, const void* indices) {
@@ -159,18 +169,20 @@ int launch_attend_tc(const MlaParams& p, cudaStream_t stream) {
     int* status = nullptr;
     e = mla_tc_status_address(&status);
     if (e != cudaSuccess) return (int)e;
-    const int R = p.tq * p.heads;
-    const dim3 grid((unsigned)(2 * p.splits), (unsigned)((R + kMlaTcRows - 1) / kMlaTcRows), (unsigned)p.batch);
-    mla_attend_tc_kernel<T><<<grid, kMlaTcThreads, MlaTcGeom::kSmemBytes, stream>>>(p, status);
+    int sms = 0;
+    e = sm_count(&sms);
+    if (e != cudaSuccess) return (int)e;
+    const int pairs = sms / 2 > 0 ? sms / 2 : 1;
+    mla_tc_plan_kernel<<<1, kMlaTcPlanThreads, 0, stream>>>(p, pairs);
     int rc = (int)cudaGetLastError();
     if (rc != 0) return rc;
-    if (p.splits > 1) {
-        const long long total = (long long)p.batch * R;
-        mla_merge_kernel<T><<<(unsigned)((total + kMlaMergeWarps - 1) / kMlaMergeWarps), kMlaMergeWarps * 32, 0,
-                              stream>>>(p, total);
-        rc = (int)cudaGetLastError();
-    }
-    return rc;
+    mla_attend_tc_kernel<T><<<2 * pairs, kMlaTcThreads, MlaTcGeom::kSmemBytes, stream>>>(p, status);
+    rc = (int)cudaGetLastError();
+    if (rc != 0) return rc;
+    const long long warps = (long long)p.tc_units * kMlaTcRows;
+    mla_tc_merge_kernel<T><<<(unsigned)((warps + kMlaMergeWarps - 1) / kMlaMergeWarps), kMlaMergeWarps * 32, 0,
+                             stream>>>(p);
+    return (int)cudaGetLastError();
 }
 
 template <typename T>
@@ -243,11 +255,10 @@ size_t mla_b200_attend_workspace_bytes(int batch, int tq, int heads, int dc, int
     const int capacity = nk > 0 ? nk : page * max_pages;
     size_t need = partial_bytes(rows, heads, dc, simt_auto_splits(rows, heads, capacity));
     if (dc == kMlaTcDc && dr == kMlaTcDr && nk == 0) {
-        int sms = 0, chunk = 0, splits = 1;
+        int sms = 0;
         if (sm_count(&sms) != cudaSuccess) sms = 148;
         const long long units = (long long)batch * (((long long)tq * heads + kMlaTcRows - 1) / kMlaTcRows);
-        tc_chunking(units, capacity, sms / 2, &chunk, &splits);
-        const size_t tc = partial_bytes(rows, heads, dc, splits);
+        const size_t tc = tc_scratch(units, capacity, sms / 2, 0).total();
         if (tc > need) need = tc;
     }
     return need > 256 ? need : 256;
@@ -290,17 +301,24 @@ int mla_b200_attend_ex(const void* q_absorbed, const void* q_rope, const void* c
         int sms = 0;
         cudaError_t e = sm_count(&sms);
         if (e != cudaSuccess) return (int)e;
+        if (splits > 32767) return GQA_B200_ERR_SPLITS;
         const long long units = (long long)batch * (((long long)tq * heads + kMlaTcRows - 1) / kMlaTcRows);
-        tc_chunking(units, capacity, sms / 2, &p.chunk_tokens, &p.splits);
-        if (splits > 0) {                            // explicit split count: equal chunks of the capacity
-            if (splits > 32767) return GQA_B200_ERR_SPLITS;
-            p.splits = splits;
-            p.chunk_tokens = ((capacity + splits - 1) / splits + kMlaTcBN - 1) / kMlaTcBN * kMlaTcBN;
-        }
+        if (units > 2147483647LL / kMlaTcRows) return GQA_B200_ERR_INT32_RANGE;
+        p.tc_units = (int)units;
+        p.tc_row_tiles = (int)(((long long)tq * heads + kMlaTcRows - 1) / kMlaTcRows);
+        p.tc_force_range = tc_force_range(capacity, splits);
+        const TcScratch t = tc_scratch(units, capacity, sms / 2 > 0 ? sms / 2 : 1, p.tc_force_range);
+        if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < t.total())
+            return GQA_B200_ERR_WORKSPACE;
+        char* ws = static_cast<char*>(workspace);
+        p.tc_sched = reinterpret_cast<int*>(ws);
+        p.part_ml = reinterpret_cast<float*>(ws + t.sched_bytes);
+        p.part_acc = reinterpret_cast<float*>(ws + t.sched_bytes + t.ml_bytes);
+        p.splits = 1;
     } else {
         p.splits = splits > 0 ? splits : simt_auto_splits(rows, heads, capacity);
     }
-    if (p.splits > 1) {
+    if (!use_tc && p.splits > 1) {
         const size_t need = partial_bytes(rows, heads, dc, p.splits);
         if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < need)
             return GQA_B200_ERR_WORKSPACE;

@@ -20,7 +20,11 @@ struct MlaParams {
     float* part_acc;           // [rows * heads][splits][dc]  unnormalised
     long long num_blocks;
     int batch, tq, heads, dc, dr, page, max_pages, nk, splits, causal;
-    int chunk_tokens;          // tensor-core kernel: tokens per split (split s covers [s, s+1) * chunk_tokens)
+    int* tc_sched;             // tensor-core kernel: [0] total tiles, [1] tiles per range, [2] ranges,
+                               //   [4 ...] prefix[u] = tiles before unit u (units + 1 entries)
+    int tc_units;              // units = batch * tc_row_tiles; a unit = 128 query rows of one sequence
+    int tc_row_tiles;          // ceil(tq * heads / 128)
+    int tc_force_range;        // > 0: tiles per range (else total / pairs)
     int page_shift;            // log2(page) when page is a power of two, else -1
     float scale_log2;          // scale * log2(e)
 };

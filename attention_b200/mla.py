@@ -150,6 +150,8 @@ def mla_latent_attention(q_absorbed, q_rope, cache, block_table, lengths, positi
                                                        q_rope.size(3), cache.size(1), block_table.size(1), nk))
         if splits > 1:   # an explicit split count may need more than the automatic one
             need = max(need, q.size(0) * q.size(1) * q.size(2) * splits * (q.size(3) + 2) * 4 + 512)
+            units = q.size(0) * ((q.size(1) * q.size(2) + 127) // 128)     # tensor-core kernel: slots
+            need = max(need, (units * (splits + 1) + 1) * 128 * (q.size(3) + 2) * 4 + (units + 5) * 4 + 1024)
         ws = _scratch(q.device, stream, need)
         rc = lib.mla_b200_attend_ex(
             q.data_ptr(), q_rope.data_ptr(), cache.data_ptr(), block_table.data_ptr(), lengths.data_ptr(),
