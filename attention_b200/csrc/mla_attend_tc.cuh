@@ -187,6 +187,8 @@ constexpr int kMlaTcMinRange = 4;       // a range is at least 4 tiles (256 toke
 __global__ void __launch_bounds__(kMlaTcPlanThreads)
 mla_tc_plan_kernel(const MlaParams p, int pairs) {
     __shared__ int s_sum[kMlaTcPlanThreads];
+    pdl_launch_dependents();
+    pdl_wait();                                      // the previous call's kernels still read the schedule
     const int tid = threadIdx.x, U = p.tc_units, R = p.tq * p.heads;
     const int per = (U + kMlaTcPlanThreads - 1) / kMlaTcPlanThreads;
     const int lo = min(U, tid * per), hi = min(U, lo + per);
@@ -224,6 +226,8 @@ mla_tc_plan_kernel(const MlaParams p, int pairs) {
 template <typename T>
 __global__ void __launch_bounds__(kMlaMergeWarps * 32)
 mla_tc_merge_kernel(const MlaParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const long long wid = (long long)blockIdx.x * kMlaMergeWarps + (threadIdx.x >> 5);
     const int u = (int)(wid / kMlaTcRows), r = (int)(wid - (long long)u * kMlaTcRows);
@@ -297,6 +301,8 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     const int col0 = rank ? 256 : 0;                 // first cache column this CTA owns
     T* op = reinterpret_cast<T*>(p.out);
 
+    pdl_launch_dependents();
+    pdl_wait();                                      // the schedule and the queries come from earlier kernels
     const uint32_t s_base = tc::smem_u32(smem);
     if (s_base & 1023u) {                            // the swizzled tiles need a 1024-byte aligned base
         if (tid == 0 && status) atomicExch(status, 3);

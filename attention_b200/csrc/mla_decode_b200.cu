@@ -7,6 +7,7 @@
 
 #include <cmath>
 #include <cstdint>
+#include <cstdlib>
 
 #include "../../include/mla_decode_b200.h"
 #include "mla_attend_tc.cuh"
@@ -37,6 +38,29 @@ cudaError_t sm_count(int* out) {
 }
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Launch with programmatic stream serialization: the kernel may start while its predecessor
+// in the stream drains; every kernel of this file executes griddepcontrol.wait before its first
+// global access, so the order of the data is kept and only launch latency overlaps.
+// GQA_B200_NO_PDL=1 in the environment turns it off.
+template <typename... KArgs, typename... Args>
+int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    static const bool no_pdl = [] {
+        const char* e = std::getenv("GQA_B200_NO_PDL");
+        return e && e[0] == '1';
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = no_pdl ? 0 : 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 // Status word of the tensor-core attention kernel: 0 ok, 2 = a bounded wait ran out, 3 = the
 // dynamic shared memory base was not 1024-byte aligned.  Read with mla_b200_tc_status.
@@ -147,9 +171,8 @@ int launch_attend_simt(const MlaParams& p, cudaStream_t stream) {
     if (rc != 0) return rc;
     if (p.splits > 1) {
         const long long total = rows * p.heads;
-        mla_merge_kernel<T><<<(unsigned)((total + kMlaMergeWarps - 1) / kMlaMergeWarps), kMlaMergeWarps * 32, 0,
-                              stream>>>(p, total);
-        rc = (int)cudaGetLastError();
+        rc = launch_pdl(mla_merge_kernel<T>, dim3((unsigned)((total + kMlaMergeWarps - 1) / kMlaMergeWarps)),
+                        dim3(kMlaMergeWarps * 32), 0, stream, p, total);
     }
     return rc;
 }
@@ -173,16 +196,14 @@ int launch_attend_tc(const MlaParams& p, cudaStream_t stream) {
     e = sm_count(&sms);
     if (e != cudaSuccess) return (int)e;
     const int pairs = sms / 2 > 0 ? sms / 2 : 1;
-    mla_tc_plan_kernel<<<1, kMlaTcPlanThreads, 0, stream>>>(p, pairs);
-    int rc = (int)cudaGetLastError();
+    int rc = launch_pdl(mla_tc_plan_kernel, dim3(1), dim3(kMlaTcPlanThreads), 0, stream, p, pairs);
     if (rc != 0) return rc;
-    mla_attend_tc_kernel<T><<<2 * pairs, kMlaTcThreads, MlaTcGeom::kSmemBytes, stream>>>(p, status);
-    rc = (int)cudaGetLastError();
+    rc = launch_pdl(mla_attend_tc_kernel<T>, dim3(2 * pairs), dim3(kMlaTcThreads), MlaTcGeom::kSmemBytes, stream, p,
+                    status);
     if (rc != 0) return rc;
     const long long warps = (long long)p.tc_units * kMlaTcRows;
-    mla_tc_merge_kernel<T><<<(unsigned)((warps + kMlaMergeWarps - 1) / kMlaMergeWarps), kMlaMergeWarps * 32, 0,
-                             stream>>>(p);
-    return (int)cudaGetLastError();
+    return launch_pdl(mla_tc_merge_kernel<T>, dim3((unsigned)((warps + kMlaMergeWarps - 1) / kMlaMergeWarps)),
+                      dim3(kMlaMergeWarps * 32), 0, stream, p);
 }
 
 template <typename T>
@@ -193,6 +214,8 @@ int launch_project(const void* x, const void* w, void* out, long long rows, int 
     const unsigned chunks = (unsigned)((rows + kProjRows - 1) / kProjRows);
     if (absorb) {
         const dim3 grid(chunks, (unsigned)((d_out + kProjThreads - 1) / kProjThreads), (unsigned)heads);
+        // (plain launches: with an early-launched successor holding shared memory on every SM
+        // these full-grid kernels ran slower)
         mla_absorb_kernel<T><<<grid, kProjThreads, smem, stream>>>(
             static_cast<const T*>(x), static_cast<const T*>(w), static_cast<T*>(out), rows, heads, d_in, d_out);
     } else {
@@ -242,9 +265,9 @@ int mla_b200_latent_kv_write(const void* latent, const void* rope, void* cache, 
     if (!latent || !rope || !cache || !slots) return GQA_B200_ERR_NULL_POINTER;
     return by_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
-        mla_cache_write_kernel<T><<<(unsigned)n, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-            static_cast<const T*>(latent), static_cast<const T*>(rope), static_cast<T*>(cache), slots, dc, dr);
-        return (int)cudaGetLastError();
+        return launch_pdl(mla_cache_write_kernel<T>, dim3((unsigned)n), dim3(128), 0, static_cast<cudaStream_t>(stream),
+                          static_cast<const T*>(latent), static_cast<const T*>(rope), static_cast<T*>(cache), slots,
+                          dc, dr);
     });
 }
 

@@ -120,6 +120,34 @@ def _check_attend(q, qr, cache, table, lens, positions, indices, scale):
                and indices.dtype == torch.int32, "indices must be int32 [B,T,K]")
 
 
+_attend_need: dict[tuple, int] = {}
+
+
+def _attend_inputs_ok(q, qr, cache, table, lens, positions, indices, scale) -> bool:
+    """One boolean for "every check below passes" (the common case); on False the caller runs the
+    detailed checks, which raise the specific message."""
+    try:
+        dev, dt = q.device, q.dtype
+        ok = (q.is_cuda and dt in _DTYPE_CODE and qr.dtype == dt and cache.dtype == dt
+              and qr.device == dev and cache.device == dev and table.device == dev and lens.device == dev
+              and positions.device == dev
+              and q.is_contiguous() and qr.is_contiguous() and cache.is_contiguous() and table.is_contiguous()
+              and lens.is_contiguous() and positions.is_contiguous()
+              and q.dim() == 4 and qr.dim() == 4 and cache.dim() == 3 and table.dim() == 2 and lens.dim() == 1
+              and positions.dim() == 2 and q.shape[:3] == qr.shape[:3]
+              and q.size(0) == table.size(0) == lens.size(0) == positions.size(0) and positions.size(1) == q.size(1)
+              and table.dtype == torch.int32 and lens.dtype == torch.int32 and positions.dtype == torch.int32
+              and 0.0 < scale < math.inf
+              and 0 < q.size(3) <= 512 and qr.size(3) > 0 and cache.size(2) == q.size(3) + qr.size(3)
+              and cache.size(0) > 0 and cache.size(1) > 0 and table.size(1) > 0 and q.size(2) > 0)
+        if ok and indices is not None:
+            ok = (indices.is_cuda and indices.device == dev and indices.is_contiguous() and indices.dim() == 3
+                  and indices.size(0) == q.size(0) and indices.size(1) == q.size(1) and indices.dtype == torch.int32)
+        return bool(ok)
+    except (AttributeError, TypeError):
+        return False
+
+
 def mla_latent_attention(q_absorbed, q_rope, cache, block_table, lengths, positions, *, scale,
                          causal=True, indices=None, kernel="auto", splits=0):
     """Latent output ``[B,T,H,Dc]``; ``indices`` are logical int32 ``[B,T,K]``.
@@ -131,11 +159,13 @@ def mla_latent_attention(q_absorbed, q_rope, cache, block_table, lengths, positi
     """
     lib = _lib()
     scale = float(scale)
-    _check_attend(q_absorbed, q_rope, cache, block_table, lengths, positions, indices, scale)
     q = q_absorbed
-    _check(q.size(3) > 0 and q.size(3) <= 512 and q_rope.size(3) > 0
-           and cache.size(2) == q.size(3) + q_rope.size(3) and cache.size(0) > 0 and cache.size(1) > 0
-           and block_table.size(1) > 0 and q.size(2) > 0, "invalid dimensions")
+    if not _attend_inputs_ok(q, q_rope, cache, block_table, lengths, positions, indices, scale):
+        _check_attend(q_absorbed, q_rope, cache, block_table, lengths, positions, indices, scale)
+        _check(q.size(3) > 0 and q.size(3) <= 512 and q_rope.size(3) > 0
+               and cache.size(2) == q.size(3) + q_rope.size(3) and cache.size(0) > 0 and cache.size(1) > 0
+               and block_table.size(1) > 0 and q.size(2) > 0, "invalid dimensions")
+        raise RuntimeError("invalid mla_latent_attention arguments")   # not reached: a check above raises
     if kernel not in _KERNEL_CODE:
         raise ValueError("kernel must be auto, simt or tcgen05")
     out = torch.empty_like(q)
@@ -146,12 +176,16 @@ def mla_latent_attention(q_absorbed, q_rope, cache, block_table, lengths, positi
         return out.zero_()
     with _on_device(q.device):
         stream = _stream_handle(q.device)
-        need = int(lib.mla_b200_attend_workspace_bytes(q.size(0), q.size(1), q.size(2), q.size(3),
-                                                       q_rope.size(3), cache.size(1), block_table.size(1), nk))
-        if splits > 1:   # an explicit split count may need more than the automatic one
-            need = max(need, q.size(0) * q.size(1) * q.size(2) * splits * (q.size(3) + 2) * 4 + 512)
-            units = q.size(0) * ((q.size(1) * q.size(2) + 127) // 128)     # tensor-core kernel: slots
-            need = max(need, (units * (splits + 1) + 1) * 128 * (q.size(3) + 2) * 4 + (units + 5) * 4 + 1024)
+        key = (q.size(0), q.size(1), q.size(2), q.size(3), q_rope.size(3), cache.size(1), block_table.size(1), nk,
+               splits)
+        need = _attend_need.get(key)
+        if need is None:
+            need = int(lib.mla_b200_attend_workspace_bytes(*key[:8]))
+            if splits > 1:   # an explicit split count may need more than the automatic one
+                need = max(need, q.size(0) * q.size(1) * q.size(2) * splits * (q.size(3) + 2) * 4 + 512)
+                units = q.size(0) * ((q.size(1) * q.size(2) + 127) // 128)     # tensor-core kernel: slots
+                need = max(need, (units * (splits + 1) + 1) * 128 * (q.size(3) + 2) * 4 + (units + 5) * 4 + 1024)
+            _attend_need[key] = need
         ws = _scratch(q.device, stream, need)
         rc = lib.mla_b200_attend_ex(
             q.data_ptr(), q_rope.data_ptr(), cache.data_ptr(), block_table.data_ptr(), lengths.data_ptr(),

@@ -245,3 +245,22 @@ def test_mla_tensor_core_kernel_refuses_other_shapes():
     with pytest.raises(RuntimeError, match="kernel"):
         attn.mla_latent_attention(qa, d["q_rope"], d["cache"], d["block_table"], d["lengths"], d["positions"],
                                   scale=0.1, kernel="tcgen05")
+
+
+@gpu
+def test_mla_tensor_core_kernel_many_ragged_sequences():
+    """More sequences than SM pairs, ragged lengths: ranges of the tile schedule start and end
+    inside sequences, several work items per CTA pair, whole-unit and partial items mixed."""
+    from attention_b200.mla import mla_tc_status
+    gen = torch.Generator().manual_seed(11)
+    lengths = torch.randint(1, 1400, (90,), generator=gen).tolist()
+    lengths[3] = 0
+    lengths[17] = 4000                                  # one long sequence spanning several ranges
+    w, c = _tc_case(16, 1, 64, lengths, torch.bfloat16, seed=12)
+    d = _dev(c)
+    got, want = _latent(c, d, "tcgen05")
+    _close(got, want, torch.bfloat16)
+    assert torch.count_nonzero(got[3]) == 0
+    again, _ = _latent(c, d, "tcgen05")
+    assert torch.equal(got, again)                      # same schedule, same order of sums: repeatable
+    assert mla_tc_status() == 0
