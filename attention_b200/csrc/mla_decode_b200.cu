@@ -11,6 +11,7 @@
 
 #include "../../include/mla_decode_b200.h"
 #include "mla_attend_tc.cuh"
+#include "mla_project_mma.cuh"
 #include "mla_simt.cuh"
 
 namespace gqa_b200 {
@@ -206,9 +207,39 @@ int launch_attend_tc(const MlaParams& p, cudaStream_t stream) {
                       dim3(kMlaMergeWarps * 32), 0, stream, p);
 }
 
+// fp16 / bf16 with both widths multiples of 64 and 16-byte aligned tensors: tensor-core kernel
+template <typename T, bool ABSORB>
+int launch_project_mma(const void* x, const void* w, void* out, long long rows, int heads, int d_in, int d_out,
+                       cudaStream_t stream) {
+    static bool ready[kMaxDevices];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+    const size_t smem = proj_mma_smem_bytes(d_in);
+    if (!ready[dev]) {
+        e = cudaFuncSetAttribute(mla_project_mma_kernel<T, ABSORB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 160 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        ready[dev] = true;
+    }
+    const dim3 grid((unsigned)((rows + kProjMmaRows - 1) / kProjMmaRows), (unsigned)(d_out / kProjMmaCols),
+                    (unsigned)heads);
+    mla_project_mma_kernel<T, ABSORB><<<grid, kProjMmaThreads, smem, stream>>>(
+        static_cast<const T*>(x), static_cast<const T*>(w), static_cast<T*>(out), rows, heads, d_in, d_out);
+    return (int)cudaGetLastError();
+}
+
 template <typename T>
 int launch_project(const void* x, const void* w, void* out, long long rows, int heads, int d_in,
                    int d_out, int absorb, cudaStream_t stream) {
+    if constexpr (!std::is_same<T, float>::value) {
+        const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) |
+                               reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+        if (aligned && d_in % 64 == 0 && d_out % 64 == 0 && proj_mma_smem_bytes(d_in) <= 160 * 1024)
+            return absorb ? launch_project_mma<T, true>(x, w, out, rows, heads, d_in, d_out, stream)
+                          : launch_project_mma<T, false>(x, w, out, rows, heads, d_in, d_out, stream);
+    }
     const size_t smem = (size_t)kProjRows * d_in * sizeof(float);
     if (smem > 48 * 1024) return GQA_B200_ERR_KERNEL;
     const unsigned chunks = (unsigned)((rows + kProjRows - 1) / kProjRows);

@@ -264,3 +264,22 @@ def test_mla_tensor_core_kernel_many_ragged_sequences():
     again, _ = _latent(c, d, "tcgen05")
     assert torch.equal(got, again)                      # same schedule, same order of sums: repeatable
     assert mla_tc_status() == 0
+
+
+@gpu
+@pytest.mark.parametrize("rows,heads,d_in,d_out,dtype", [
+    (3, 5, 128, 512, torch.bfloat16),      # W_uk-like, one partial row tile
+    (70, 2, 64, 64, torch.float16),        # two row tiles, the second ragged
+    (64, 3, 512, 128, torch.bfloat16),     # W_uv-like
+    (130, 1, 192, 192, torch.float16),
+])
+def test_mla_projections_tensor_core_path(rows, heads, d_in, d_out, dtype):
+    """Widths that are multiples of 64 take the mma.sync projection kernel; both directions."""
+    gen = torch.Generator().manual_seed(rows + d_in)
+    x = (torch.randn(rows, 1, heads, d_in, generator=gen)).to(dtype)
+    w_absorb = (torch.randn(heads, d_in, d_out, generator=gen) / math.sqrt(d_in)).to(dtype)
+    w_value = (torch.randn(heads, d_out, d_in, generator=gen) / math.sqrt(d_in)).to(dtype)
+    got = attn.mla_query_absorb(x.to(DEV), w_absorb.to(DEV))
+    _close(got, mla_oracle.reference_mla_project(x, w_absorb, True), dtype)
+    got = attn.mla_value_project(x.to(DEV), w_value.to(DEV))
+    _close(got, mla_oracle.reference_mla_project(x, w_value, False), dtype)
