@@ -165,10 +165,13 @@ def mla_cases(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    mla_cases(sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--") else "/root/reference")
+    paths = [a for a in sys.argv[1:] if not a.startswith("--")]
+    if not paths:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference [--mla-only | --prefill-only]")
+    mla_cases(paths[0])
     if "--mla-only" in sys.argv:
         sys.exit(0)
-    prefill_cases(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    prefill_cases(paths[0])
     if "--prefill-only" in sys.argv:
         sys.exit(0)
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(paths[0])
