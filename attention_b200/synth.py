@@ -182,6 +182,8 @@ MLA_WORKLOADS = {
                                          torch.bfloat16, 1024, 4096),
     "m3_deepseek_h16_bf16": MlaWorkload("m3_deepseek_h16_bf16", 128, 1, 16, 128, 64, 512, 128, 64,
                                         torch.bfloat16, 1024, 8192),
+    "m4_deepseek_h128_long_bf16": MlaWorkload("m4_deepseek_h128_long_bf16", 16, 1, 128, 128, 64, 512, 128, 64,
+                                              torch.bfloat16, 16384, 65536),
 }
 
 
