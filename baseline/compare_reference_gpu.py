@@ -100,8 +100,12 @@ def compare_prefill(ref):
 def compare_mla(ref):
     """Paged latent (MLA) decode: this library vs the reference's fused CUDA operator
     (attention/mla.py:43-53) on the synthetic MLA workloads."""
-    for name in ("m2_deepseek_h128_bf16", "m3_deepseek_h16_bf16"):
-        w = synth.MLA_WORKLOADS[name]
+    # the shapes of the reference's own MLA decode timing (benchmarks/bench_tensorcore_followup.py:25-28:
+    # one sequence, 4 heads, Dn 32, Dr 16, Dc 64, Dv 32, page 16, bf16, L = 512 / 1024 / 4096)
+    small = {f"ref_bench_L{n}": synth.MlaWorkload(f"ref_bench_L{n}", 1, 1, 4, 32, 16, 64, 32, 16, torch.bfloat16, n, n)
+             for n in (512, 1024, 4096)}
+    for name in ("m2_deepseek_h128_bf16", "m3_deepseek_h16_bf16", *small):
+        w = small.get(name) or synth.MLA_WORKLOADS[name]
         c = synth.make_mla_case(w, seed=42, device="cuda", cache_on_device=True)
         nbytes = synth.mla_algorithmic_bytes(c["lengths"].cpu(), w)
         args = (c["q_nope"], c["q_rope"], c["cache"], c["block_table"], c["lengths"], c["positions"],
