@@ -197,6 +197,35 @@ def mla_latent_attention(q_absorbed, q_rope, cache, block_table, lengths, positi
     return out
 
 
+_decode_need: dict[tuple, int] = {}
+
+
+def _decode_inputs_ok(q, qr, cache, table, lens, positions, w_uk, w_uv, indices, scale) -> bool:
+    """One boolean for "every check of mla_decode passes" (the common case)."""
+    try:
+        dev, dt = q.device, q.dtype
+        dc = w_uk.size(2)
+        ok = (q.is_cuda and dt in _DTYPE_CODE and qr.dtype == dt and cache.dtype == dt and w_uk.dtype == dt
+              and w_uv.dtype == dt
+              and all(t.device == dev and t.is_contiguous()
+                      for t in (q, qr, cache, table, lens, positions, w_uk, w_uv))
+              and q.dim() == 4 and qr.dim() == 4 and cache.dim() == 3 and table.dim() == 2 and lens.dim() == 1
+              and positions.dim() == 2 and w_uk.dim() == 3 and w_uv.dim() == 3 and q.shape[:3] == qr.shape[:3]
+              and q.size(0) == table.size(0) == lens.size(0) == positions.size(0) and positions.size(1) == q.size(1)
+              and table.dtype == torch.int32 and lens.dtype == torch.int32 and positions.dtype == torch.int32
+              and 0.0 < scale < math.inf
+              and q.size(2) > 0 and q.size(3) > 0 and qr.size(3) > 0 and 0 < dc <= 512 and w_uv.size(1) > 0
+              and w_uk.size(0) == q.size(2) and w_uk.size(1) == q.size(3) and w_uv.size(0) == q.size(2)
+              and w_uv.size(2) == dc and cache.size(2) == dc + qr.size(3) and cache.size(0) > 0
+              and cache.size(1) > 0 and table.size(1) > 0)
+        if ok and indices is not None:
+            ok = (indices.is_cuda and indices.device == dev and indices.is_contiguous() and indices.dim() == 3
+                  and indices.size(0) == q.size(0) and indices.size(1) == q.size(1) and indices.dtype == torch.int32)
+        return bool(ok)
+    except (AttributeError, TypeError):
+        return False
+
+
 def mla_decode(q_nope, q_rope, cache, block_table, lengths, positions, w_uk, w_uv, *, scale=None,
                causal=True, indices=None):
     """Absorbed paged MLA for decode or multiple queries; pre-applied RoPE.  ``[B,T,H,Dv]``.
@@ -208,16 +237,25 @@ def mla_decode(q_nope, q_rope, cache, block_table, lengths, positions, w_uk, w_u
     if scale is None:
         scale = 1.0 / math.sqrt(q_nope.shape[-1] + q_rope.shape[-1])
     scale = float(scale)
+    q = q_nope
+    if _decode_inputs_ok(q, q_rope, cache, block_table, lengths, positions, w_uk, w_uv, indices, scale):
+        return _mla_decode_checked(lib, q, q_rope, cache, block_table, lengths, positions, w_uk, w_uv, scale,
+                                   causal, indices)
     _check_attend(q_nope, q_rope, cache, block_table, lengths, positions, indices, scale)
     _same_device(q_nope, ("w_uk", w_uk), ("w_uv", w_uv))
     _check(w_uk.dim() == 3 and w_uv.dim() == 3, "invalid tensor ranks")
-    q = q_nope
     dc = w_uk.size(2)
     _check(q.size(2) > 0 and q.size(3) > 0 and q_rope.size(3) > 0 and 0 < dc <= 512 and w_uv.size(1) > 0
            and w_uk.size(0) == q.size(2) and w_uk.size(1) == q.size(3) and w_uv.size(0) == q.size(2)
            and w_uv.size(2) == dc and cache.size(2) == dc + q_rope.size(3) and cache.size(0) > 0
            and cache.size(1) > 0 and block_table.size(1) > 0, "invalid dimensions")
     _check(q.dtype == w_uk.dtype == w_uv.dtype, "dtype mismatch")
+    raise RuntimeError("invalid mla_decode arguments")   # not reached: a check above raises
+
+
+def _mla_decode_checked(lib, q, q_rope, cache, block_table, lengths, positions, w_uk, w_uv, scale, causal,
+                        indices):
+    dc = w_uk.size(2)
     out = torch.empty((q.size(0), q.size(1), q.size(2), w_uv.size(1)), dtype=q.dtype, device=q.device)
     if out.numel() == 0:
         return out
@@ -226,8 +264,10 @@ def mla_decode(q_nope, q_rope, cache, block_table, lengths, positions, w_uk, w_u
         return out.zero_()
     with _on_device(q.device):
         stream = _stream_handle(q.device)
-        need = int(lib.mla_b200_decode_workspace_bytes(q.size(0), q.size(1), q.size(2), dc, q_rope.size(3),
-                                                       cache.size(1), block_table.size(1), nk))
+        key = (q.size(0), q.size(1), q.size(2), dc, q_rope.size(3), cache.size(1), block_table.size(1), nk)
+        need = _decode_need.get(key)
+        if need is None:
+            need = _decode_need[key] = int(lib.mla_b200_decode_workspace_bytes(*key))
         ws = _scratch(q.device, stream, need)
         rc = lib.mla_b200_decode(
             q.data_ptr(), q_rope.data_ptr(), cache.data_ptr(), block_table.data_ptr(), lengths.data_ptr(),
