@@ -225,9 +225,9 @@ int launch_project_mma(const void* x, const void* w, void* out, long long rows, 
     }
     const dim3 grid((unsigned)((rows + kProjMmaRows - 1) / kProjMmaRows), (unsigned)(d_out / kProjMmaCols),
                     (unsigned)heads);
-    mla_project_mma_kernel<T, ABSORB><<<grid, kProjMmaThreads, smem, stream>>>(
-        static_cast<const T*>(x), static_cast<const T*>(w), static_cast<T*>(out), rows, heads, d_in, d_out);
-    return (int)cudaGetLastError();
+    return launch_pdl(mla_project_mma_kernel<T, ABSORB>, grid, dim3(kProjMmaThreads), smem, stream,
+                      static_cast<const T*>(x), static_cast<const T*>(w), static_cast<T*>(out), rows, heads, d_in,
+                      d_out);
 }
 
 template <typename T>
