@@ -66,7 +66,7 @@ def parse_args():
     p.add_argument("--chunk-tokens", type=int, default=0)
     p.add_argument("--cpu-seconds", type=float, default=10.0,
                    help="target CPU time of the cpu_baseline sample")
-    p.add_argument("--spinup-seconds", type=float, default=0.3,
+    p.add_argument("--spinup-seconds", type=float, default=1.0,
                    help="extra untimed warm-up so the SM clock is out of idle")
     p.add_argument("--scaling", choices=["weak", "strong"], default="weak",
                    help="weak: every GPU gets its own batch of the workload (default); strong: "
