@@ -362,6 +362,12 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     const int t0 = seg_lo * BN;
     const int t1 = min(end_max, seg_hi * BN);
     const int n_tiles = seg_hi - seg_lo;
+    // With few heads most of the 128 rows are padding.  A softmax warp whose 32 rows hold no
+    // query row takes no part in the item (its rows of Q, S, P and O are never read by anyone);
+    // the barrier counts and the bytes expected from the peer cover the live warps only.
+    const int live_quads = min(4, (min(R - g0, BM) + 31) / 32);
+    const int live_warps = 2 * live_quads;
+    const uint32_t x_bytes = (uint32_t)live_warps * 32u * (uint32_t)(kMlaTcBN / 2) * 4u;
     const long long grow = (long long)b * R + g;     // global query row (softmax threads)
 
     if (tid == 0) {
@@ -373,16 +379,16 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         for (int i = 0; i < NS; ++i) { tc::mbar_init(bar_full + i * 8, NL); tc::mbar_init(bar_empty + i * 8, 1); }
 #pragma unroll
         for (int i = 0; i < NSB; ++i) tc::mbar_init(bar_s0 + i * 8, 1);
-        tc::mbar_init(bar_p, NT / 32);               // one arrival per softmax warp
-        tc::mbar_init(bar_q, NT / 32);
+        tc::mbar_init(bar_p, live_warps);            // one arrival per live softmax warp
+        tc::mbar_init(bar_q, live_warps);
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             tc::mbar_init(bar_x + i * 8, 1);         // one local arrival announcing the bytes per tile
-            tc::mbar_init(bar_free + i * 8, NT / 32);   // one arrival per peer softmax warp
+            tc::mbar_init(bar_free + i * 8, live_warps);   // one arrival per live softmax warp of the peer
         }
         tc::fence_mbar_init();
-        tc::mbar_arrive_expect_tx(bar_x, G::kXBytes);                          // tile 0
-        if (n_tiles > 1) tc::mbar_arrive_expect_tx(bar_x + 8, G::kXBytes);     // tile 1
+        tc::mbar_arrive_expect_tx(bar_x, x_bytes);                             // tile 0
+        if (n_tiles > 1) tc::mbar_arrive_expect_tx(bar_x + 8, x_bytes);        // tile 1
     }
     first_item = false;
     tc::tc_fence_before();
@@ -548,7 +554,9 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         const int my_end = g < R ? mla_row_end(p, b, g / p.heads) : 0;
         const int my_stop = min(my_end, t1);         // this row sees tokens [t0, my_stop) of the chunk
         float m_run = -INFINITY, l_run = 0.f;
+        const bool warp_live = quad < live_quads;
 
+        if (warp_live) {
         // ---- latent part of Q_r: global -> registers -> tensor memory.  This thread writes half of
         //      its row (16 columns = 32 elements per step); rows past the last query row are zero ----
         {
@@ -633,7 +641,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             // announce the bytes of tile j + 2 on the same barrier; they cannot land before every
             // warp here has passed the wait above, because the peer sends them only after all
             // warps have released the buffer below
-            if (tid == 0 && j + 2 < n_tiles) tc::mbar_arrive_expect_tx(bar_x + (j & 1) * 8, G::kXBytes);
+            if (tid == 0 && j + 2 < n_tiles) tc::mbar_arrive_expect_tx(bar_x + (j & 1) * 8, x_bytes);
             // this thread's half of the row; the two threads of a row swap their maxima through
             // shared memory when the two warps of the lane quadrant meet.  After that meeting both
             // have read S(j) and the landing buffer: the buffer goes back to the peer, and P(j) may
@@ -692,6 +700,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         }
         wait_bar(bar_empty + ((n_tiles - 1) % NS) * 8, ((n_tiles - 1) / NS) & 1);
         tc::tc_fence_after();
+        }   // live warps
 
         // ---- row sum = the two halves (exchanged through an idle landing buffer); store ----
         float* s_half = reinterpret_cast<float*>(smem + G::kOffX);      // [2][128], landing buffer 0 is idle
@@ -702,6 +711,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         float* pacc = p.part_acc + ((long long)slot * BM + row_l) * kMlaTcDc + col0;
 #pragma unroll
         for (int c0 = hf * 128; c0 < (hf + 1) * 128; c0 += 32) {
+            if (!warp_live) break;
             uint32_t o[32];
             tc::tmem_ld32(tmem_o + lane_sel + c0, o);
             tc::tmem_ld_wait();
