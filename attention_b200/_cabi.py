@@ -32,6 +32,7 @@ SIGNATURES = {
     "mla_b200_project": (c_int, [_P] * 3 + [c_int, c_int64] + [c_int] * 4 + [_P]),
     "mla_b200_latent_kv_write": (c_int, [_P] * 4 + [c_int64, c_int, c_int, c_int, _P]),
     "mla_b200_attend_workspace_bytes": (c_size_t, [c_int] * 8),
+    "mla_b200_attend_ex_workspace_bytes": (c_size_t, [c_int] * 9),
     "mla_b200_attend": (c_int, [_P] * 8 + [c_int] * 6 + [c_int64, c_int, c_int, c_int, c_float, c_int,
                                                          _P, c_size_t, _P]),
     "mla_b200_attend_ex": (c_int, [_P] * 8 + [c_int] * 6 + [c_int64, c_int, c_int, c_int, c_float, c_int,

@@ -2,6 +2,7 @@
 // carving, kernel selection and launches.  No allocation, no synchronisation,
 // no exceptions cross this boundary.
 #include "../../include/gqa_decode_b200.h"
+#include "../../include/mla_decode_b200.h"
 
 #include <cmath>
 #include <cstdlib>
@@ -33,14 +34,15 @@ struct DeviceInfo {
     bool ready = false;
 };
 DeviceInfo g_dev[kMaxDevices];
+std::mutex g_dev_mutex;
 
-// Device properties are read once per device (two cudaDeviceGetAttribute calls;
-// benign if two threads race to fill the same slot with the same values).
+// Device properties are read once per device (two cudaDeviceGetAttribute calls).
 cudaError_t device_info(DeviceInfo** out) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
     DeviceInfo& d = g_dev[dev];
     if (!d.ready) {
         e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
@@ -289,19 +291,6 @@ cudaError_t launch_mma_for_dim(const DecodeParams& p, int max_ctas, long long it
     switch (p.head_dim) {
         case 64:  return launch_mma<T, 64, 32, 3, 2>(p, max_ctas, item_bound, stream);
         case 128:
-#ifdef GQA_B200_TUNING
-            switch (getenv("GQA_B200_VARIANT") ? atoi(getenv("GQA_B200_VARIANT")) : 0) {
-                case 1: return launch_mma<T, 128, 16, 2, 3>(p, max_ctas, item_bound, stream);
-                case 2: return launch_mma<T, 128, 16, 3, 1, 8>(p, max_ctas, item_bound, stream);
-                case 3: return launch_mma<T, 128, 16, 2, 2, 6>(p, max_ctas, item_bound, stream);
-                case 4: return launch_mma<T, 128, 16, 4, 1, 6>(p, max_ctas, item_bound, stream);
-                case 5: return launch_mma<T, 128, 16, 2, 2>(p, max_ctas, item_bound, stream);
-                case 6: return launch_mma<T, 128, 32, 3, 1>(p, max_ctas, item_bound, stream);
-                case 10: return launch_mma<T, 128, 16, 3, 2, 4, 0>(p, max_ctas, item_bound, stream);
-                case 14: return launch_mma<T, 128, 16, 3, 2, 4, 4>(p, max_ctas, item_bound, stream);
-                default: break;
-            }
-#endif
             return launch_mma<T, 128, 16, 3, 2>(p, max_ctas, item_bound, stream);
         case 256: return launch_mma<T, 256, 16, 3, 1>(p, max_ctas, item_bound, stream);
         default:  return cudaErrorInvalidValue;
@@ -399,7 +388,7 @@ cudaError_t launch_merge_t(const DecodeParams& p, cudaStream_t stream) {
         const unsigned grid = (unsigned)((pairs + kMergeWarps - 1) / kMergeWarps);
         return launch_kernel(gqa_merge_warp_kernel<T>, dim3(grid), kMergeWarps * 32, 0, stream, p);
     }
-    const dim3 grid((unsigned)p.q_heads, (unsigned)p.batch);
+    const dim3 grid((unsigned)((long long)p.batch * p.q_heads));   // <= INT_MAX by check_common
     if (vec4) return launch_kernel(gqa_merge_kernel<T, true>, grid, kMergeWarps * 32, 0, stream, p);
     return launch_kernel(gqa_merge_kernel<T, false>, grid, kMergeWarps * 32, 0, stream, p);
 }
@@ -440,8 +429,8 @@ const char* gqa_b200_strerror(int code) {
         case GQA_B200_ERR_STATIC_LIMIT:
             return "shape needs more scratch than gqa_b200_decode_static's built-in "
                    "GQA_B200_STATIC_SCRATCH_BYTES; use gqa_b200_decode with a caller workspace";
-        case -32: return "MLA: a width, head count, tq or nk is not positive";   // MLA_B200_ERR_SHAPE
-        case -33: return "MLA: supported latent width dc is [1, 512]";           // MLA_B200_ERR_LATENT_DIM
+        case MLA_B200_ERR_SHAPE: return "MLA: a width, head count, tq or nk is not positive";
+        case MLA_B200_ERR_LATENT_DIM: return "MLA: supported latent width dc is [1, 512]";
         default: break;
     }
     if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
@@ -683,12 +672,14 @@ cudaError_t launch_prefill_mma(const PrefillParams& p, cudaStream_t stream) {
 // dynamic shared memory base was not 1024-byte aligned.  Read with gqa_b200_prefill_tc_status.
 static __device__ int g_prefill_tc_status;
 static int* g_prefill_tc_status_ptr[kMaxDevices];
+static std::mutex g_prefill_tc_status_mutex;
 
 cudaError_t prefill_tc_status_address(int** out) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_prefill_tc_status_mutex);
     if (!g_prefill_tc_status_ptr[dev]) {
         void* ptr = nullptr;
         e = cudaGetSymbolAddress(&ptr, g_prefill_tc_status);

@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(kPlanThreads) gqa_plan_kernel(const DecodePara
 
 constexpr int kMergeWarps = 4;
 
-// One CTA per (query head, sequence).  Sequences with one chunk were written by
+// One CTA per (sequence, query head).  Sequences with one chunk were written by
 // the decode kernel; empty sequences get their zero row here
 // (csrc/cuda/dense/gqa_decode.cu:65,86); the rest fold their partials:
 //   out = sum_c 2^(m_c - M) acc_c / sum_c 2^(m_c - M) l_c,  M = max_c m_c,
@@ -129,7 +129,8 @@ template <typename T, bool VEC4>
 __global__ void __launch_bounds__(kMergeWarps * 32) gqa_merge_kernel(const DecodeParams p) {
     pdl_launch_dependents();
     pdl_wait();
-    const int hq = blockIdx.x, b = blockIdx.y;
+    // 1-D grid of batch * q_heads CTAs (no 65535 limit on the batch)
+    const int b = blockIdx.x / p.q_heads, hq = blockIdx.x - b * p.q_heads;
     const int D = p.head_dim;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     T* out = reinterpret_cast<T*>(p.out) + ((size_t)b * p.q_heads + hq) * D;

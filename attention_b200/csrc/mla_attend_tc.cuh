@@ -703,8 +703,11 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         }   // live warps
 
         // ---- row sum = the two halves (exchanged through an idle landing buffer); store ----
-        float* s_half = reinterpret_cast<float*>(smem + G::kOffX);      // [2][128], landing buffer 0 is idle
-        s_half[hf * BM + row_l] = l_run;
+        // Landing buffer 0 is idle only for warps that consumed every tile of the item: a warp
+        // whose rows are all padding skipped the tile loop and may get here while the peer CTA
+        // still sends tile 0 into that buffer, so it must not write there (its value is never read).
+        float* s_half = reinterpret_cast<float*>(smem + G::kOffX);      // [2][128]
+        if (warp_live) s_half[hf * BM + row_l] = l_run;
         asm volatile("bar.sync 1, %0;" ::"n"(kMlaTcSoftmaxThreads) : "memory");   // softmax warps only
         const float l_tot = l_run + s_half[(hf ^ 1) * BM + row_l];
         const float inv = final_out ? (l_tot > 0.f ? 1.f / l_tot : 0.f) : 1.f;

@@ -8,6 +8,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstdlib>
+#include <mutex>
 
 #include "../../include/mla_decode_b200.h"
 #include "mla_attend_tc.cuh"
@@ -22,12 +23,14 @@ constexpr int kMlaMaxSplits = 32;
 constexpr int kMlaMinTokensPerSplit = 64;
 
 int g_sm_count[kMaxDevices];
+std::mutex g_mla_cache_mutex;   // guards the per-device caches of this file
 
 cudaError_t sm_count(int* out) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_mla_cache_mutex);
     if (g_sm_count[dev] == 0) {
         int n = 0;
         e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
@@ -74,6 +77,7 @@ cudaError_t mla_tc_status_address(int** out) {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_mla_cache_mutex);
     if (!g_mla_tc_status_ptr[dev]) {
         void* ptr = nullptr;
         e = cudaGetSymbolAddress(&ptr, g_mla_tc_status);
@@ -133,6 +137,19 @@ size_t partial_bytes(long long rows, int heads, int dc, int splits) {
     return align_up(n * 2 * sizeof(float), 256) + align_up(n * dc * sizeof(float), 256);
 }
 
+// Scratch the two attention paths need; the size queries and mla_b200_attend_ex both use these.
+size_t simt_scratch_bytes(int batch, int tq, int heads, int dc, int capacity, int splits) {
+    const long long rows = (long long)batch * tq;
+    return partial_bytes(rows, heads, dc, splits > 0 ? splits : simt_auto_splits(rows, heads, capacity));
+}
+long long tc_unit_count(int batch, int tq, int heads) {
+    return (long long)batch * (((long long)tq * heads + kMlaTcRows - 1) / kMlaTcRows);
+}
+size_t tc_scratch_bytes(int batch, int tq, int heads, int capacity, int sms, int splits) {
+    return tc_scratch(tc_unit_count(batch, tq, heads), capacity, sms / 2 > 0 ? sms / 2 : 1,
+                      tc_force_range(capacity, splits)).total();
+}
+
 int check_attend_shape(int dtype, int batch, int tq, int heads, int dc, int dr, long long num_blocks,
                        int page, int max_pages, int nk) {
     if (dtype != GQA_B200_F32 && dtype != GQA_B200_F16 && dtype != GQA_B200_BF16) return GQA_B200_ERR_DTYPE;
@@ -184,11 +201,15 @@ int launch_attend_tc(const MlaParams& p, cudaStream_t stream) {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     constexpr int slot = std::is_same<T, __half>::value ? 0 : 1;
-    if (!g_mla_tc_ready[dev][slot]) {
-        e = cudaFuncSetAttribute(mla_attend_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 MlaTcGeom::kSmemBytes);
-        if (e != cudaSuccess) return (int)e;
-        g_mla_tc_ready[dev][slot] = true;
+    if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+    {
+        std::lock_guard<std::mutex> lock(g_mla_cache_mutex);
+        if (!g_mla_tc_ready[dev][slot]) {
+            e = cudaFuncSetAttribute(mla_attend_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     MlaTcGeom::kSmemBytes);
+            if (e != cudaSuccess) return (int)e;
+            g_mla_tc_ready[dev][slot] = true;
+        }
     }
     int* status = nullptr;
     e = mla_tc_status_address(&status);
@@ -217,11 +238,14 @@ int launch_project_mma(const void* x, const void* w, void* out, long long rows, 
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
     const size_t smem = proj_mma_smem_bytes(d_in);
-    if (!ready[dev]) {
-        e = cudaFuncSetAttribute(mla_project_mma_kernel<T, ABSORB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 160 * 1024);
-        if (e != cudaSuccess) return (int)e;
-        ready[dev] = true;
+    {
+        std::lock_guard<std::mutex> lock(g_mla_cache_mutex);
+        if (!ready[dev]) {
+            e = cudaFuncSetAttribute(mla_project_mma_kernel<T, ABSORB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     160 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            ready[dev] = true;
+        }
     }
     const dim3 grid((unsigned)((rows + kProjMmaRows - 1) / kProjMmaRows), (unsigned)(d_out / kProjMmaCols),
                     (unsigned)heads);
@@ -302,20 +326,30 @@ int mla_b200_latent_kv_write(const void* latent, const void* rope, void* cache, 
     });
 }
 
-size_t mla_b200_attend_workspace_bytes(int batch, int tq, int heads, int dc, int dr, int page,
-                                       int max_pages, int nk) {
+size_t mla_b200_attend_ex_workspace_bytes(int batch, int tq, int heads, int dc, int dr, int page,
+                                          int max_pages, int nk, int splits) {
     if (check_attend_shape(GQA_B200_F32, batch, tq, heads, dc, dr, 1, page, max_pages, nk) != 0) return 0;
-    const long long rows = (long long)batch * tq;
-    const int capacity = nk > 0 ? nk : page * max_pages;
-    size_t need = partial_bytes(rows, heads, dc, simt_auto_splits(rows, heads, capacity));
-    if (dc == kMlaTcDc && dr == kMlaTcDr && nk == 0) {
+    if (splits < 0 || splits > 65535) return 0;
+    // Whether `indices` will be passed is not known here, so the answer covers both kernels
+    // mla_b200_attend_ex may take for this shape: the SIMT kernel (dense, or index-selected
+    // over nk entries) and, for the tensor-core shape, the dense tensor-core kernel.
+    size_t need = simt_scratch_bytes(batch, tq, heads, dc, page * max_pages, splits);
+    if (nk > 0) {
+        const size_t sel = simt_scratch_bytes(batch, tq, heads, dc, nk, splits);
+        if (sel > need) need = sel;
+    }
+    if (dc == kMlaTcDc && dr == kMlaTcDr && splits <= 32767) {
         int sms = 0;
         if (sm_count(&sms) != cudaSuccess) sms = 148;
-        const long long units = (long long)batch * (((long long)tq * heads + kMlaTcRows - 1) / kMlaTcRows);
-        const size_t tc = tc_scratch(units, capacity, sms / 2, 0).total();
+        const size_t tc = tc_scratch_bytes(batch, tq, heads, page * max_pages, sms, splits);
         if (tc > need) need = tc;
     }
     return need > 256 ? need : 256;
+}
+
+size_t mla_b200_attend_workspace_bytes(int batch, int tq, int heads, int dc, int dr, int page,
+                                       int max_pages, int nk) {
+    return mla_b200_attend_ex_workspace_bytes(batch, tq, heads, dc, dr, page, max_pages, nk, 0);
 }
 
 int mla_b200_attend_ex(const void* q_absorbed, const void* q_rope, const void* cache,
@@ -356,7 +390,7 @@ int mla_b200_attend_ex(const void* q_absorbed, const void* q_rope, const void* c
         cudaError_t e = sm_count(&sms);
         if (e != cudaSuccess) return (int)e;
         if (splits > 32767) return GQA_B200_ERR_SPLITS;
-        const long long units = (long long)batch * (((long long)tq * heads + kMlaTcRows - 1) / kMlaTcRows);
+        const long long units = tc_unit_count(batch, tq, heads);
         if (units > 2147483647LL / kMlaTcRows) return GQA_B200_ERR_INT32_RANGE;
         p.tc_units = (int)units;
         p.tc_row_tiles = (int)(((long long)tq * heads + kMlaTcRows - 1) / kMlaTcRows);
@@ -373,7 +407,7 @@ int mla_b200_attend_ex(const void* q_absorbed, const void* q_rope, const void* c
         p.splits = splits > 0 ? splits : simt_auto_splits(rows, heads, capacity);
     }
     if (!use_tc && p.splits > 1) {
-        const size_t need = partial_bytes(rows, heads, dc, p.splits);
+        const size_t need = simt_scratch_bytes(batch, tq, heads, dc, capacity, p.splits);
         if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < need)
             return GQA_B200_ERR_WORKSPACE;
         const size_t n = (size_t)rows * heads * p.splits;

@@ -1,7 +1,7 @@
 // tcgen05 (5th-generation tensor core) / TMEM / mbarrier helpers as inline PTX for
-// sm_100a.  Every wait is bounded: mbar_wait gives up after max_iters polls and
-// returns false, so a missing arrival ends a kernel with an error status instead of
-// hanging the GPU.
+// sm_100a.  Every wait is bounded in time: mbar_wait polls until %globaltimer says
+// max_ns nanoseconds have passed and then returns false, so a missing arrival ends a
+// kernel with an error status instead of hanging the GPU.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>

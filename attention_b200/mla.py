@@ -180,11 +180,7 @@ def mla_latent_attention(q_absorbed, q_rope, cache, block_table, lengths, positi
                splits)
         need = _attend_need.get(key)
         if need is None:
-            need = int(lib.mla_b200_attend_workspace_bytes(*key[:8]))
-            if splits > 1:   # an explicit split count may need more than the automatic one
-                need = max(need, q.size(0) * q.size(1) * q.size(2) * splits * (q.size(3) + 2) * 4 + 512)
-                units = q.size(0) * ((q.size(1) * q.size(2) + 127) // 128)     # tensor-core kernel: slots
-                need = max(need, (units * (splits + 1) + 1) * 128 * (q.size(3) + 2) * 4 + (units + 5) * 4 + 1024)
+            need = int(lib.mla_b200_attend_ex_workspace_bytes(*key[:8], int(splits)))
             _attend_need[key] = need
         ws = _scratch(q.device, stream, need)
         rc = lib.mla_b200_attend_ex(

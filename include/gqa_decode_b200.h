@@ -2,9 +2,11 @@
  * gqa_decode_b200.h -- C ABI of the B200 (sm_100a) paged grouped-query decode library.
  *
  * Every entry point takes plain pointers and sizes, never allocates or frees
- * device memory, never synchronises the device, never throws, and returns an
- * int status: 0 = ok, < 0 = invalid argument (see gqa_b200_strerror), > 0 = a
- * cudaError_t raised by a launch.  All device pointers must belong to the
+ * device memory, never throws, and returns an int status: 0 = ok, < 0 = invalid
+ * argument (see gqa_b200_strerror), > 0 = a cudaError_t raised by a launch.  No
+ * entry point synchronises the device, with two exceptions that say so below:
+ * the debug getters gqa_b200_prefill_tc_status and mla_b200_tc_status, which
+ * copy a status word back with a blocking cudaMemcpy.  All device pointers must belong to the
  * device that is current in the calling thread; work is enqueued on `stream`
  * (a cudaStream_t passed as void*; NULL = the legacy default stream).
  *

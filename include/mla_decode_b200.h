@@ -2,8 +2,9 @@
  * mla_decode_b200.h -- C ABI of the B200 (sm_100a) paged latent-attention (MLA) decode path.
  *
  * Exported by the same shared library as gqa_decode_b200.h and under the same
- * rules: plain pointers and sizes, no allocation, no device synchronisation, no
- * exceptions; every function returns an int status (0 = ok, < 0 = one of the
+ * rules: plain pointers and sizes, no allocation, no device synchronisation
+ * (except the debug getter mla_b200_tc_status), no exceptions; every function
+ * returns an int status (0 = ok, < 0 = one of the
  * GQA_B200_ERR_* codes of gqa_decode_b200.h or an MLA_B200_ERR_* code below,
  * > 0 = a cudaError_t); gqa_b200_strerror() gives the text for all of them.
  * Work is enqueued on `stream` (a cudaStream_t passed as void*).
@@ -63,7 +64,8 @@ GQA_B200_API int mla_b200_latent_kv_write(const void* latent, const void* rope, 
                                           int dtype, void* stream);
 
 /* Bytes of scratch mla_b200_attend needs for this shape (256-byte aligned base).
- * nk = 0 for dense attention.  Returns 0 for an invalid shape. */
+ * nk = 0 for dense attention; with nk > 0 the answer covers a call with and without
+ * `indices`.  Returns 0 for an invalid shape. */
 GQA_B200_API size_t mla_b200_attend_workspace_bytes(int batch, int tq, int heads, int dc, int dr,
                                                     int page, int max_pages, int nk);
 
@@ -78,6 +80,11 @@ GQA_B200_API int mla_b200_attend(const void* q_absorbed, const void* q_rope, con
                                  int dtype, int batch, int tq, int heads, int dc, int dr,
                                  int64_t num_blocks, int page, int max_pages, int nk, float scale,
                                  int causal, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Bytes of scratch mla_b200_attend_ex needs for this shape and split count (0 =
+ * automatic), whichever kernel it takes and whether or not `indices` is passed. */
+GQA_B200_API size_t mla_b200_attend_ex_workspace_bytes(int batch, int tq, int heads, int dc, int dr,
+                                                       int page, int max_pages, int nk, int splits);
 
 /* Same with an explicit kernel (MLA_B200_KERNEL_*) and split count (0 = automatic). */
 GQA_B200_API int mla_b200_attend_ex(const void* q_absorbed, const void* q_rope, const void* cache,

@@ -70,6 +70,18 @@ def test_golden_seeded_forced_chunks(name, chunk):
     _assert_close(got, want, q.dtype, f"{name} chunk={chunk}")
 
 
+def test_reference_import_name_runs_the_same_kernels():
+    """The reference's callers write `import attention; attention.gqa_decode(*tensors)`
+    positionally (benchmarks/bench_gqa_decode.py:43)."""
+    import attention
+    (q, k, v, table, lens), want = load_seeded("seed_c2_small_bf16")
+    tensors = _cuda(q, k, v, table, lens)
+    got = attention.gqa_decode(*tensors)
+    _assert_close(got, want, q.dtype, "import attention")
+    assert torch.equal(got, attn.gqa_decode(*tensors))
+    assert attention.is_cuda_extension_loaded()
+
+
 # --------------------------------------------------------------------------- edge grid
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("bs", [1, 8, 16, 32, 64, 5, 24])

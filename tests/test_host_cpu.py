@@ -121,6 +121,25 @@ def test_product_never_imports_the_oracle():
     for path in list((ROOT / "attention_b200").rglob("*.py")) + list((ROOT / "attention_b200").rglob("*.cu*")):
         text = path.read_text()
         assert "oracle" not in text.lower() or path.name == "synth.py", path
+    text = (ROOT / "attention" / "__init__.py").read_text()
+    assert "import oracle" not in text and "from oracle" not in text
+
+
+def test_reference_import_name_exposes_the_rebuilt_path():
+    """`import attention; attention.gqa_decode(...)` is the reference's entry point
+    (attention/__init__.py:2-19); here the name resolves to the B200 library."""
+    import attention
+    assert attention.gqa_decode is attn.gqa_decode
+    for name in ("gqa_decode", "gqa_decode_split", "gqa_decode_auto", "gqa_prefill", "kv_append",
+                 "is_cuda_extension_loaded", "latent_kv_write", "mla_query_absorb",
+                 "mla_value_project", "mla_latent_attention", "mla_decode", "sparse_mla"):
+        assert callable(getattr(attention, name)), name
+        assert name in attention.__all__
+    assert not hasattr(attention, "reference_gqa_decode")     # the checker is not shipped
+    q, k, v, table, lens = synth.make_workload(
+        synth.scaled("c1_cpu_fp32", batch=2, len_lo=8, len_hi=20), seed=1)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):    # still no CPU fallback
+        attention.gqa_decode(q, k, v, table, lens)
 
 
 def test_validate_paged_metadata():

@@ -6,8 +6,11 @@ synchronisation is not acceptable, or their host runtime owns device memory.
 For them the library carries an 8 MiB scratch array of its own.  This test calls
 that entry point directly through the C ABI, twice in a row on different inputs
 (the array is shared and keeps the previous call's contents), and checks each
-result against the ordinary entry point, which gets a workspace from the caller.
-It also checks that a shape too large for the built-in array is refused cleanly.
+result against the ordinary entry point, which gets a workspace from the caller:
+both run the same plan, decode and merge on the same inputs, so the results must
+be equal bit for bit.  It also checks that the free device memory does not move
+across a call, and that the size limit is enforced from both sides: a shape whose
+scratch need is just inside the built-in array runs, one just outside is refused.
 
 The file name sorts last on purpose: with ``-x`` every other test has already
 run when this one does.  It does not depend on them and passes on its own.
@@ -15,8 +18,6 @@ run when this one does.  It does not depend on them and passes on its own.
 
 import pytest
 import torch
-
-from conftest import TOL
 
 from attention_b200 import _cabi, synth
 
@@ -63,13 +64,59 @@ def test_static_scratch_entry_point_matches_the_ordinary_one_twice_in_a_row():
         rc, got = _decode_static(lib, *inputs)
         assert rc == 0, _cabi.strerror(rc)
         torch.cuda.synchronize()
-        tol = TOL[w.dtype]
-        torch.testing.assert_close(got.float(), want.float(), atol=tol, rtol=tol)
-        # same inputs again straight away: stale scratch from the call before must not matter
-        rc, again = _decode_static(lib, *inputs)
-        assert rc == 0
+        assert torch.equal(got, want)
+        # same inputs again straight away: stale scratch from the call before must not matter,
+        # and the call must leave the amount of free device memory where it was
+        out = torch.full_like(inputs[0], float("nan"))
+        stream = torch.cuda.current_stream().cuda_stream
+        args = _args(*inputs, out)
         torch.cuda.synchronize()
-        torch.testing.assert_close(again.float(), want.float(), atol=tol, rtol=tol)
+        free_before = torch.cuda.mem_get_info()[0]
+        rc = lib.gqa_b200_decode_static(*args, stream)
+        torch.cuda.synchronize()
+        free_after = torch.cuda.mem_get_info()[0]
+        assert rc == 0
+        assert free_after == free_before, "the static entry point must not allocate device memory"
+        assert torch.equal(out, want)
+
+
+def test_static_scratch_limit_from_both_sides():
+    """The widest block table whose worst-case scratch still fits the built-in array is
+    accepted (and gives the ordinary entry point's bits); one page more is refused."""
+    lib = _cabi.load()
+    w = synth.scaled("c2_qwen3_8b_bf16", batch=8, len_lo=100, len_hi=900)
+    q, k, v, table, lens = synth.make_workload(w, seed=5, device=DEV, kv_on_device=True)
+    limit = 8 << 20
+
+    def need(pages):
+        return lib.gqa_b200_workspace_bytes(w.batch, w.q_heads, w.kv_heads, w.head_dim, w.block_size,
+                                            pages, 0)
+
+    lo, hi = table.size(1), 1 << 22            # need(lo) fits, need(hi) does not
+    assert need(lo) <= limit < need(hi)
+    while hi - lo > 1:                         # need() is monotone in the table width
+        mid = (lo + hi) // 2
+        if need(mid) <= limit:
+            lo = mid
+        else:
+            hi = mid
+    assert need(lo) <= limit < need(lo + 1)
+
+    def widened(pages):
+        t = torch.full((w.batch, pages), -1, dtype=torch.int32, device=DEV)
+        t[:, : table.size(1)] = table
+        return t
+
+    inside, outside = widened(lo), widened(lo + 1)
+    want = _decode_with_caller_workspace(lib, q, k, v, inside, lens)
+    rc, got = _decode_static(lib, q, k, v, inside, lens)
+    assert rc == 0, _cabi.strerror(rc)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    rc, out = _decode_static(lib, q, k, v, outside, lens)
+    assert rc == STATIC_LIMIT
+    torch.cuda.synchronize()
+    assert torch.isnan(out.float()).all()          # nothing was launched
 
 
 def test_static_scratch_entry_point_refuses_shapes_beyond_its_limit():
