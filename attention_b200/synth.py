@@ -88,8 +88,30 @@ def pool_blocks_for(w: DecodeWorkload, lens: torch.Tensor) -> int:
     return max(1, math.ceil(w.pool_factor * need))
 
 
+def threaded_normal(shape, dtype: torch.dtype, seed: int, threads: int = 0) -> torch.Tensor:
+    """A CPU tensor of N(0,1) draws filled by several threads, each with its own seeded
+    generator over a fixed slice (deterministic for a given seed, whatever the thread count).
+    One generator fills about 40 M elements a second; multi-GB page pools for the timed CPU
+    baseline would otherwise take most of a minute to draw."""
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+    out = torch.empty(shape, dtype=dtype)
+    flat = out.view(-1)
+    n = flat.numel()
+    step = 1 << 24
+    threads = threads or len(os.sched_getaffinity(0))
+
+    def fill(i):
+        g = torch.Generator().manual_seed(seed * 1000003 + i)
+        flat[i * step:(i + 1) * step].normal_(generator=g)
+
+    with ThreadPoolExecutor(max(1, threads)) as ex:
+        list(ex.map(fill, range((n + step - 1) // step)))
+    return out
+
+
 def _draw_tensors(w: DecodeWorkload, lens: torch.Tensor, gen: torch.Generator, seed: int, device,
-                  kv_on_device: bool):
+                  kv_on_device: bool, kv_threaded: bool = False):
     """q, K, V and the page table for given lengths, drawn in that order from ``gen``."""
     q = torch.randn(w.batch, w.q_heads, w.head_dim, generator=gen, dtype=torch.float32)
     pool = pool_blocks_for(w, lens)
@@ -98,6 +120,9 @@ def _draw_tensors(w: DecodeWorkload, lens: torch.Tensor, gen: torch.Generator, s
         dgen = torch.Generator(device=device).manual_seed(seed)
         k = torch.empty(shape, dtype=w.dtype, device=device).normal_(generator=dgen)
         v = torch.empty(shape, dtype=w.dtype, device=device).normal_(generator=dgen)
+    elif kv_threaded:
+        k = threaded_normal(shape, w.dtype, 2 * seed).to(device)
+        v = threaded_normal(shape, w.dtype, 2 * seed + 1).to(device)
     else:
         k = torch.randn(shape, generator=gen, dtype=torch.float32).to(w.dtype).to(device)
         v = torch.randn(shape, generator=gen, dtype=torch.float32).to(w.dtype).to(device)
@@ -124,16 +149,17 @@ def make_workload(w: DecodeWorkload | str, *, seed: int = 42, device="cpu",
 
 
 def make_workload_for_lengths(w: DecodeWorkload | str, lens: torch.Tensor, *, seed: int = 42,
-                              device="cpu", kv_on_device: bool = False):
+                              device="cpu", kv_on_device: bool = False, kv_threaded: bool = False):
     """Like ``make_workload`` but for given context lengths (e.g. one rank's share of a batch):
     batch = len(lens), a private page pool of ``pool_factor`` x the pages those lengths need.
+    ``kv_threaded`` draws CPU page pools with ``threaded_normal`` (fast, for timing baselines).
     Returns (the resized workload, the five tensors)."""
     if isinstance(w, str):
         w = WORKLOADS[w]
     lens = lens.to(torch.int32).cpu()
     w = replace(w, batch=int(lens.numel()), fixed_pool_blocks=0)
     gen = torch.Generator(device="cpu").manual_seed(seed)
-    return w, _draw_tensors(w, lens, gen, seed, device, kv_on_device)
+    return w, _draw_tensors(w, lens, gen, seed, device, kv_on_device, kv_threaded)
 
 
 def scaled(w: DecodeWorkload | str, **changes) -> DecodeWorkload:
