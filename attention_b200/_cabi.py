@@ -18,6 +18,8 @@ SIGNATURES = {
     "gqa_b200_max_chunks_per_seq": (c_int, [c_int, c_int, c_int]),
     "gqa_b200_auto_chunk_tokens": (c_int, [c_int, c_int, c_int, c_int, c_int]),
     "gqa_b200_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
+    "gqa_b200_workspace_control_bytes": (c_size_t, []),
+    "gqa_b200_workspace_init": (c_int, [_P, c_size_t, _P]),
     "gqa_b200_decode": (c_int, [_P] * 6 + [c_int] * 5 + [c_int64, c_int, c_int, c_float, _P,
                                                           c_size_t, _P]),
     "gqa_b200_decode_ex": (c_int, [_P] * 6 + [c_int] * 5 + [c_int64, c_int, c_int, c_float, _P,

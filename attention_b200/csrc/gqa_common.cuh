@@ -18,6 +18,11 @@ constexpr int kHdrCounter = 0;
 constexpr int kHdrTotalChunks = 1;
 constexpr int kHdrStatus = 2;
 constexpr int kHdrChunkBase = 3;
+constexpr int kHdrDone = 4;             // CTAs that have left the decode kernel (self-cleaning)
+constexpr int kFusedMaxBatch = 2048;    // one-launch mode keeps a [batch + 1] prefix array in shared memory
+constexpr int kFusedMaxTickets = 16384; // arrival counters at a FIXED place and size in every workspace, so
+                                        // that a call of one shape cannot scribble partials over what a
+                                        // later call of another shape takes for its (zero) tickets
 constexpr int kNumAutoBases = 5;        // adaptive base candidates: 1024 >> i, i = 0..4
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -53,7 +58,12 @@ inline int max_chunks_for_capacity(long long cap, int base) {
 // ---------------------------------------------------------------------------
 // Launch parameters shared by the plan, decode and merge kernels.
 // ---------------------------------------------------------------------------
-enum : int { kModePlanned = 0, kModeRefSplits = 1 };
+// kModePlanned   plan kernel -> decode kernel -> merge kernel (three launches)
+// kModeRefSplits caller-chosen split count, the reference's partial layout
+// kModeFused     ONE launch: every decode CTA derives the chunk list from context_lens
+//                itself, and the CTA that finishes the last chunk of a (sequence, kv head,
+//                head group) folds that group's partials into `out`
+enum : int { kModePlanned = 0, kModeRefSplits = 1, kModeFused = 2 };
 
 struct DecodeParams {
     const void* q;
@@ -68,6 +78,7 @@ struct DecodeParams {
     int4* items;            // [cap_chunks] (sequence, partial slot | single<<30, t0, t1)
     float2* part_ml;        // [cap_chunks * q_heads] (max in log2 units, sum)
     float* part_acc;        // [cap_chunks * q_heads * head_dim]
+    int32_t* tickets;       // fused mode: [batch * kv_heads * head_groups] arrival counts, zero between calls
     int cap_chunks;
     int item_target;        // adaptive base: smallest chunk total that fills the resident CTAs
     // reference-split mode
@@ -102,6 +113,7 @@ __device__ __forceinline__ int clamp_len(const DecodeParams& p, int b) {
     return len > p.cap_tokens ? p.cap_tokens : len;
 }
 
+// (planned and reference-split modes; the fused mode counts its items in fused_plan)
 __device__ __forceinline__ int total_items(const DecodeParams& p) {
     const int per = p.kv_heads * p.head_groups;
     if (p.mode == kModePlanned) {
@@ -278,7 +290,7 @@ __device__ __forceinline__ void combine_and_store(const DecodeParams& p, const W
             } else {
                 dst[0] = from_f32<T>(a0 * inv);
             }
-        } else if (p.mode == kModePlanned) {
+        } else if (p.mode != kModeRefSplits) {
             const size_t slot = (size_t)w.part_slot * p.q_heads + hq;
             float* dst = p.part_acc + slot * D + col;
             if (VEC4) *reinterpret_cast<float4*>(dst) = make_float4(a0, a1, a2, a3);

@@ -60,7 +60,8 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 inline int elem_size(int dtype) { return dtype == GQA_B200_F32 ? 4 : 2; }
 
 struct WorkspaceLayout {
-    size_t hdr, chunk_off, items, part_ml, part_acc, total;
+    size_t hdr, tickets, chunk_off, items, part_ml, part_acc, total;
+    size_t control_bytes;   // header + tickets: the part that must be zero before the first call
     int cap_chunks;
 };
 
@@ -87,7 +88,13 @@ WorkspaceLayout workspace_layout(int batch, int q_heads, int kv_heads, int head_
     long long cap;
     if (chunk_base == 0) {
         cap = nb * max_chunks_for_capacity(cap_tokens, 1024);
-        const long long dyn = 2ll * item_target_chunks(q_heads, kv_heads) + nb;
+        // room for the finer bases the device may pick: eight waves of items over the resident
+        // CTAs (the one-launch kernel only considers bases whose chunk total fits), never less
+        // than the plan kernel's own bound of twice its item target
+        const long long per = (long long)kv_heads * (((q_heads / kv_heads) + 15) / 16);
+        long long dyn = (8ll * kAssumedCtaSlots + per - 1) / per + nb;
+        const long long plan_bound = 2ll * item_target_chunks(q_heads, kv_heads) + nb;
+        if (plan_bound > dyn) dyn = plan_bound;
         const long long finest = nb * max_chunks_for_capacity(cap_tokens, 1024 >> (kNumAutoBases - 1));
         const long long other = dyn < finest ? dyn : finest;
         if (other > cap) cap = other;
@@ -99,6 +106,9 @@ WorkspaceLayout workspace_layout(int batch, int q_heads, int kv_heads, int head_
     w.cap_chunks = (int)cap;
     size_t at = 0;
     w.hdr = at;        at = align_up(at + kHdrWords * sizeof(int32_t), 256);
+    // one ticket per (sequence, kv head, head group); a fixed region whatever the shape
+    w.tickets = at;    at = align_up(at + (size_t)kFusedMaxTickets * sizeof(int32_t), 256);
+    w.control_bytes = at;
     w.chunk_off = at;  at = align_up(at + ((size_t)batch + 1) * sizeof(int32_t), 256);
     w.items = at;      at = align_up(at + (size_t)cap * sizeof(int4), 256);
     w.part_ml = at;    at = align_up(at + (size_t)cap * q_heads * sizeof(float2), 256);
@@ -258,6 +268,13 @@ cudaError_t launch_kernel(KernelT kernel, dim3 grid, int threads, size_t smem, c
     return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
+// Shared memory of the one-launch mode's [batch + 1] prefix array, in steps of 1 KB so that
+// the occupancy cache sees few distinct sizes.
+inline size_t fused_prefix_bytes(const DecodeParams& p) {
+    if (p.mode != kModeFused) return 0;
+    return align_up(((size_t)p.batch + 1) * sizeof(int), 1024);
+}
+
 template <typename KernelT>
 cudaError_t launch_persistent(KernelT kernel, const DecodeParams& p, int threads, size_t smem,
                               int max_ctas, long long item_bound, cudaStream_t stream) {
@@ -280,7 +297,7 @@ template <typename T, int D, int TILE_N, int NSTAGES, int MIN_CTAS, int NWARPS =
 cudaError_t launch_mma(const DecodeParams& p, int max_ctas, long long item_bound,
                        cudaStream_t stream) {
     using G = MmaGeom<D, TILE_N, NSTAGES, NWARPS>;
-    const size_t smem = G::kFixedBytes + (size_t)p.table_smem_entries * sizeof(int);
+    const size_t smem = G::kFixedBytes + (size_t)p.table_smem_entries * sizeof(int) + fused_prefix_bytes(p);
     return launch_persistent(gqa_decode_mma_kernel<T, D, TILE_N, NSTAGES, NWARPS, MIN_CTAS, CP_MODE>, p,
                              NWARPS * 32, smem, max_ctas, item_bound, stream);
 }
@@ -302,7 +319,7 @@ cudaError_t launch_simt(const DecodeParams& p, int max_ctas, long long item_boun
                         cudaStream_t stream) {
     const int o_stride = ((p.head_dim + 3) & ~3) + 4;
     const size_t smem = ((size_t)kSimtWarps * GB * o_stride + 2 * kSimtWarps * GB) * sizeof(float) +
-                        (size_t)p.table_smem_entries * sizeof(int);
+                        (size_t)p.table_smem_entries * sizeof(int) + fused_prefix_bytes(p);
     return launch_persistent(gqa_decode_simt_kernel<T, EPL, CONTIG, GB>, p, kSimtWarps * 32, smem,
                              max_ctas, item_bound, stream);
 }
@@ -354,8 +371,8 @@ cudaError_t launch_decode_t(DecodeParams& p, bool use_mma, int max_ctas, cudaStr
         p.heads_per_item = simt_heads_per_item(p.head_dim, p.group);
     }
     p.head_groups = (p.group + p.heads_per_item - 1) / p.heads_per_item;
-    long long parts = p.mode == kModePlanned ? (long long)p.cap_chunks
-                                             : (long long)p.batch * p.splits;
+    long long parts = p.mode == kModeRefSplits ? (long long)p.batch * p.splits
+                                               : (long long)p.cap_chunks;
     long long item_bound = parts * p.kv_heads * p.head_groups;
     if (item_bound > 0x7fffffffll) return cudaErrorInvalidValue;
     if (use_mma) {
@@ -466,6 +483,17 @@ size_t gqa_b200_workspace_bytes(int batch, int q_heads, int kv_heads, int head_d
     return workspace_layout(batch, q_heads, kv_heads, head_dim, block_size, max_pages, base).total;
 }
 
+size_t gqa_b200_workspace_control_bytes(void) {
+    return workspace_layout(1, 1, 1, 1, 1, 1, 0).control_bytes;
+}
+
+int gqa_b200_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+    const size_t control = gqa_b200_workspace_control_bytes();
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < control)
+        return GQA_B200_ERR_WORKSPACE;
+    return (int)cudaMemsetAsync(workspace, 0, control, static_cast<cudaStream_t>(stream));
+}
+
 int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
                        const int32_t* block_table, const int32_t* context_lens, void* out,
                        int dtype, int batch, int q_heads, int kv_heads, int head_dim,
@@ -493,6 +521,7 @@ int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
                head_dim, num_blocks, block_size, max_pages, scale);
     char* ws = static_cast<char*>(workspace);
     p.hdr = reinterpret_cast<int32_t*>(ws + lay.hdr);
+    p.tickets = reinterpret_cast<int32_t*>(ws + lay.tickets);
     p.chunk_off = reinterpret_cast<int32_t*>(ws + lay.chunk_off);
     p.items = reinterpret_cast<int4*>(ws + lay.items);
     p.part_ml = reinterpret_cast<float2*>(ws + lay.part_ml);
@@ -509,6 +538,13 @@ int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
     if (kernel == GQA_B200_KERNEL_SIMT) use_mma = false;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // (the SIMT kernel's groups of four query heads are the finest grouping any kernel uses)
+    const long long ticket_count = (long long)batch * kv_heads * ((q_heads / kv_heads + 3) / 4);
+    if (phases == 0 && batch <= kFusedMaxBatch && ticket_count <= kFusedMaxTickets) {
+        // one launch: the decode kernel plans for itself and the last chunk of a sequence merges
+        p.mode = kModeFused;
+        return (int)launch_decode(p, dtype, use_mma, max_ctas, s);
+    }
     if (phases == 0) phases = GQA_B200_PHASE_PLAN | GQA_B200_PHASE_DECODE | GQA_B200_PHASE_MERGE;
     cudaError_t e = cudaSuccess;
     if (phases & GQA_B200_PHASE_PLAN) {
@@ -579,9 +615,9 @@ int gqa_b200_decode_static(const void* q, const void* k_cache, const void* v_cac
     void* scratch = nullptr;
     const cudaError_t e = static_scratch_address(&scratch);
     if (e != cudaSuccess) return (int)e;
-    // Nothing in the scratch has to start at zero: the plan kernel rewrites the
-    // header (work counter included), the item list and the prefix array on every
-    // call, and partial slots are written before the merge kernel reads them.
+    // The control words (work counter, tickets) must be zero when a call starts: the
+    // array is zero when the module is loaded, and every call leaves them at zero.
+    // Partial slots are written before they are read.
     return gqa_b200_decode_ex(q, k_cache, v_cache, block_table, context_lens, out, dtype, batch,
                               q_heads, kv_heads, head_dim, num_blocks, block_size, max_pages, scale,
                               scratch, kStaticScratchBytes, stream, 0, GQA_B200_KERNEL_AUTO, 0, 0);

@@ -18,6 +18,7 @@
 #pragma once
 
 #include "gqa_common.cuh"
+#include "gqa_fused.cuh"
 
 namespace gqa_b200 {
 
@@ -151,7 +152,10 @@ gqa_decode_mma_kernel(const DecodeParams p) {
     float* s_m = reinterpret_cast<float*>(s_q + G::kQBytes);            // [NWARPS][16]
     float* s_l = s_m + NWARPS * 16;                                     // [NWARPS][16]
     int* s_table = reinterpret_cast<int*>(s_l + NWARPS * 16);           // [table_smem_entries]
+    int* s_off = s_table + p.table_smem_entries;                         // fused mode: [batch + 1]
     __shared__ int s_item;
+    __shared__ int s_flag;
+    __shared__ int s_red[2 * kNumAutoBases * 32 + 32];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r0 = lane >> 2;            // fragment row (and row + 8)
@@ -165,8 +169,19 @@ gqa_decode_mma_kernel(const DecodeParams p) {
     const long long row_bytes_all = (long long)p.kv_heads * ROWB;   // one token, all kv heads
     const uint64_t policy = CP_MODE >= 3 ? evict_first_policy() : 0;
     pdl_launch_dependents();
-    pdl_wait();   // the plan kernel wrote hdr / items
-    const int n_items = total_items(p);
+    pdl_wait();   // the plan kernel wrote hdr / items; the call before left the counters at zero
+    const bool fused = p.mode == kModeFused;
+    const bool counted = p.mode != kModeRefSplits;      // items are pulled from the work counter
+    FusedPlan plan;
+    plan.base = p.chunk_base;
+    plan.total_chunks = 0;
+    int n_items;
+    if (fused) {
+        plan = fused_plan<NWARPS * 32>(p, s_off, s_red);
+        n_items = plan.total_chunks * p.kv_heads * p.head_groups;
+    } else {
+        n_items = total_items(p);
+    }
 
     // per-lane constants of the tile copy: row within a pass and 16-byte chunk
     const int ld_row = lane / CPR;
@@ -180,7 +195,7 @@ gqa_decode_mma_kernel(const DecodeParams p) {
     const bool pages_hold_subtiles = p.bs_shift >= 4;
 
     int item;
-    if (p.mode == kModePlanned) {
+    if (counted) {
         if (tid == 0) s_item = atomicAdd(p.hdr + kHdrCounter, 1);
         __syncthreads();
         item = s_item;
@@ -188,16 +203,20 @@ gqa_decode_mma_kernel(const DecodeParams p) {
         item = blockIdx.x;
     }
     int4 rec = make_int4(0, 0, 0, 0);
-    if (item < n_items) rec = load_item_record(p, item);
+    if (!fused && item < n_items) rec = load_item_record(p, item);
+    // one-launch mode: the ticket of the item before (taken at its end, looked at one item later)
+    bool pend = false;
+    WorkItem pend_w{};
+    int pend_rows = 0, pend_old = 0;
 
     while (item < n_items) {
         int next = 0;
-        if (p.mode == kModePlanned) {
+        if (counted) {
             if (tid == 0) next = atomicAdd(p.hdr + kHdrCounter, 1);
         } else {
             next = item + gridDim.x;
         }
-        const WorkItem w = item_from_record(p, item, rec);
+        const WorkItem w = fused ? fused_item(p, item, s_off, plan.base) : item_from_record(p, item, rec);
         const int rows_valid = min(16, p.group - w.hg * 16);
         const bool nonempty = w.t1 > w.t0;
 
@@ -446,7 +465,7 @@ gqa_decode_mma_kernel(const DecodeParams p) {
         // fetch the next item's record now; its latency hides behind the combine
         const int nxt = s_item;
         int4 rec_next = make_int4(0, 0, 0, 0);
-        if (nxt < n_items) rec_next = load_item_record(p, nxt);
+        if (!fused && nxt < n_items) rec_next = load_item_record(p, nxt);
         if (nonempty) {
             combine_and_store<T, NWARPS, true>(p, w, reinterpret_cast<const float*>(s_ring),
                                                G::kWarpBytes / 4, G::kOStride, s_m, s_l, 16,
@@ -454,10 +473,22 @@ gqa_decode_mma_kernel(const DecodeParams p) {
         } else {
             store_empty<T>(p, w, rows_valid);
         }
-        __syncthreads();   // rings, Q tile, table and s_item are free again
+        const bool multi = fused && nonempty && w.n_parts > 1;
+        if (multi) __threadfence();   // this thread's partial stores are visible device-wide ...
+        __syncthreads();   // ... for the whole CTA; rings, Q tile, table and s_item are free again
+        if (pend)
+            fused_resolve_ticket<T>(p, pend_w, pend_rows, pend_old, &s_flag, s_ring, NWARPS * G::kWarpBytes);
+        pend = multi;
+        if (multi) {
+            if (tid == 0) pend_old = atomicAdd(fused_ticket(p, w), 1);
+            pend_w = w;
+            pend_rows = rows_valid;
+        }
         item = nxt;
         rec = rec_next;
     }
+    if (pend) fused_resolve_ticket<T>(p, pend_w, pend_rows, pend_old, &s_flag, s_ring, NWARPS * G::kWarpBytes);
+    if (counted) decode_counters_release(p, plan.total_chunks, plan.base);
 }
 
 }  // namespace gqa_b200

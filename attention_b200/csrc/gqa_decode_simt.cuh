@@ -11,6 +11,7 @@
 #pragma once
 
 #include "gqa_common.cuh"
+#include "gqa_fused.cuh"
 
 namespace gqa_b200 {
 
@@ -63,19 +64,33 @@ gqa_decode_simt_kernel(const DecodeParams p) {
     float* s_m = s_o + NW * GB * o_stride;                       // [NW][GB]
     float* s_l = s_m + NW * GB;                                  // [NW][GB]
     int* s_table = reinterpret_cast<int*>(s_l + NW * GB);        // [table_smem_entries]
+    int* s_off = s_table + p.table_smem_entries;                 // fused mode: [batch + 1]
     __shared__ int s_item;
+    __shared__ int s_flag;
+    __shared__ int s_red[2 * kNumAutoBases * 32 + 32];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const T* kc = reinterpret_cast<const T*>(p.k);
     const T* vc = reinterpret_cast<const T*>(p.v);
     const T* qp = reinterpret_cast<const T*>(p.q);
     pdl_launch_dependents();
-    pdl_wait();   // the plan kernel wrote hdr / items
-    const int n_items = total_items(p);
+    pdl_wait();   // the plan kernel wrote hdr / items; the call before left the counters at zero
+    const bool fused = p.mode == kModeFused;
+    const bool counted = p.mode != kModeRefSplits;      // items are pulled from the work counter
+    FusedPlan plan;
+    plan.base = p.chunk_base;
+    plan.total_chunks = 0;
+    int n_items;
+    if (fused) {
+        plan = fused_plan<NW * 32>(p, s_off, s_red);
+        n_items = plan.total_chunks * p.kv_heads * p.head_groups;
+    } else {
+        n_items = total_items(p);
+    }
     const long long row_elems = (long long)p.kv_heads * D;
 
     int item;
-    if (p.mode == kModePlanned) {
+    if (counted) {
         if (tid == 0) s_item = atomicAdd(p.hdr + kHdrCounter, 1);
         __syncthreads();
         item = s_item;
@@ -84,12 +99,12 @@ gqa_decode_simt_kernel(const DecodeParams p) {
     }
     while (item < n_items) {
         int next = 0;
-        if (p.mode == kModePlanned) {
+        if (counted) {
             if (tid == 0) next = atomicAdd(p.hdr + kHdrCounter, 1);
         } else {
             next = item + gridDim.x;
         }
-        const WorkItem w = decode_item(p, item);
+        const WorkItem w = fused ? fused_item(p, item, s_off, plan.base) : decode_item(p, item);
         const int rows_valid = min(GB, p.group - w.hg * GB);
 
         if (w.t1 <= w.t0) {
@@ -122,9 +137,10 @@ gqa_decode_simt_kernel(const DecodeParams p) {
                 __syncthreads();   // previous segment's table no longer in use
                 stage_table(p, w.b, s0, s1, s_table, first_page);
                 __syncthreads();
-                for (int tb = s0 + warp * TOK; tb < s1; tb += NW * TOK) {
-                    float kx[TOK][EPL], vx[TOK][EPL];
-                    bool valid[TOK];
+                // rows of the warp's next TOK tokens are requested before the current ones are
+                // used (register double buffer): an item of a few iterations is otherwise a chain
+                // of dependent memory round trips
+                auto load_tokens = [&](int tb, float (&kx)[TOK][EPL], float (&vx)[TOK][EPL], bool (&valid)[TOK]) {
 #pragma unroll
                     for (int tk = 0; tk < TOK; ++tk) {
                         const int t = tb + tk;
@@ -142,6 +158,21 @@ gqa_decode_simt_kernel(const DecodeParams p) {
                             for (int j = 0; j < EPL; ++j) { kx[tk][j] = 0.f; vx[tk][j] = 0.f; }
                         }
                     }
+                };
+                float kn[TOK][EPL], vn[TOK][EPL];
+                bool validn[TOK];
+                int tb = s0 + warp * TOK;
+                if (tb < s1) load_tokens(tb, kn, vn, validn);
+                for (; tb < s1; tb += NW * TOK) {
+                    float kx[TOK][EPL], vx[TOK][EPL];
+                    bool valid[TOK];
+#pragma unroll
+                    for (int tk = 0; tk < TOK; ++tk) {
+                        valid[tk] = validn[tk];
+#pragma unroll
+                        for (int j = 0; j < EPL; ++j) { kx[tk][j] = kn[tk][j]; vx[tk][j] = vn[tk][j]; }
+                    }
+                    if (tb + NW * TOK < s1) load_tokens(tb + NW * TOK, kn, vn, validn);
 #pragma unroll
                     for (int g = 0; g < GB; ++g) {
                         if (g >= rows_valid) continue;
@@ -193,9 +224,10 @@ gqa_decode_simt_kernel(const DecodeParams p) {
             __syncthreads();
             combine_and_store<T, NW, VEC4>(p, w, s_o, GB * o_stride, o_stride, s_m, s_l, GB,
                                            rows_valid);
+            if (fused && w.n_parts > 1) fused_finish_item<T, VEC4>(p, w, rows_valid, &s_flag);
         }
         __syncthreads();
-        if (p.mode == kModePlanned) {
+        if (counted) {
             if (tid == 0) s_item = next;
             __syncthreads();
             item = s_item;
@@ -203,6 +235,7 @@ gqa_decode_simt_kernel(const DecodeParams p) {
             item = next;
         }
     }
+    if (counted) decode_counters_release(p, plan.total_chunks, plan.base);
 }
 
 }  // namespace gqa_b200

@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(kPlanThreads) gqa_plan_kernel(const DecodePara
         p.chunk_off[p.batch] = run_n;
         p.hdr[kHdrTotalChunks] = run_n;
         p.hdr[kHdrCounter] = 0;
+        p.hdr[kHdrDone] = 0;
         p.hdr[kHdrStatus] = run_n > p.cap_chunks ? 1 : 0;
         p.hdr[kHdrChunkBase] = base_tokens;
     }

@@ -18,7 +18,11 @@ import math
 import torch
 
 from .core import (_DTYPE_CODE, _check, _check_cuda_contiguous, _lib, _on_device, _raise_status,
-                   _stream_handle, _workspaces)
+                   _stream_handle)
+
+# (device index, stream handle) -> uint8 scratch tensor of the MLA operators.  Kept apart from
+# the GQA decode workspaces: those carry control words that must stay zero between calls.
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
 
 _KERNEL_CODE = {"auto": 0, "simt": 1, "tcgen05": 4}
 

@@ -30,7 +30,7 @@ extern "C" {
 
 #define GQA_B200_API __attribute__((visibility("default")))
 
-#define GQA_B200_ABI_VERSION 1
+#define GQA_B200_ABI_VERSION 2
 
 /* element types of q / k_cache / v_cache / out */
 #define GQA_B200_F32 0
@@ -65,7 +65,7 @@ extern "C" {
 
 /* Workspace header: the first int32 words of the workspace, readable by the
  * host after a stream synchronise when debugging.
- *   word 0  work-item counter of the last launch
+ *   word 0  work-item counter (zero between calls)
  *   word 1  number of (sequence, chunk) pairs the last plan produced
  *   word 2  device status: 0 ok, 1 = plan overflowed the workspace (cannot
  *           happen when it is sized by gqa_b200_workspace_bytes)
@@ -103,20 +103,38 @@ GQA_B200_API int gqa_b200_max_chunks_per_seq(int max_pages, int block_size, int 
 
 /* Bytes of device scratch gqa_b200_decode / _decode_ex need for this static
  * shape (worst case over context_lens).  The buffer must be 256-byte aligned.
- * Its contents need no initialisation and carry nothing between calls; two
- * calls that may overlap on the device need two workspaces. */
+ * Its control words -- the first gqa_b200_workspace_control_bytes() bytes,
+ * whatever the shape: a header and the arrival counters of the one-launch
+ * path -- must be ZERO before the first call that uses it: cudaMemset the
+ * buffer once after allocating it, or call gqa_b200_workspace_init.  Every
+ * call leaves those words at zero again, so a workspace is initialised once,
+ * not per call, and may be reused by calls of other shapes that fit in it.
+ * Nothing else carries over between calls.  Two calls that may overlap on the
+ * device need two workspaces. */
 GQA_B200_API size_t gqa_b200_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim,
                                              int block_size, int max_pages, int chunk_tokens);
+
+/* Size of the control region at the start of every workspace (about 64 KB). */
+GQA_B200_API size_t gqa_b200_workspace_control_bytes(void);
+
+/* Zero the control words of a workspace (one cudaMemsetAsync on `stream`; no
+ * allocation, no synchronisation).  Needed once per workspace, and again only
+ * if something else wrote into the buffer or a call was torn down by a CUDA
+ * error. */
+GQA_B200_API int gqa_b200_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
 
 /* Paged single-token MHA/MQA/GQA decode.
  * Replaces gqa_decode_cuda (csrc/binding/torch_ops.cpp:5-11,
  * csrc/cuda/dense/gqa_decode.cu:186-188) and, through it, gqa_decode_impl
  * (gqa_decode.cu:96-183) with its two kernels (gqa_decode.cu:18-87).
- * Three launches on `stream`: plan (cuts sequences into KV chunks on the
- * device, no host read of context_lens), decode (persistent CTAs pull
- * (sequence, chunk, kv head) items; every K/V row is read once for all query
- * heads of its group), merge (log-sum-exp fold of the chunk partials; also
- * writes the zero rows of empty sequences).
+ * ONE launch on `stream` for batches of up to 2048 sequences (and at most
+ * 16384 (sequence, kv head) pairs): every persistent
+ * decode CTA cuts the sequences into KV chunks itself from context_lens (never
+ * read by the host), pulls (sequence, chunk, kv head) items from a counter --
+ * every K/V row is read once for all query heads of its group -- and the CTA
+ * that finishes the last chunk of a sequence folds that sequence's partials
+ * (log-sum-exp, in slot order) into `out`.  Larger batches take three launches:
+ * plan, decode, merge.  Empty sequences get zero rows.
  * batch == 0 returns OK without launching (gqa_decode.cu:142). */
 GQA_B200_API int gqa_b200_decode(const void* q, const void* k_cache, const void* v_cache,
                                  const int32_t* block_table, const int32_t* context_lens,
@@ -125,7 +143,8 @@ GQA_B200_API int gqa_b200_decode(const void* q, const void* k_cache, const void*
                                  float scale, void* workspace, size_t workspace_bytes,
                                  void* stream);
 
-/* phases of gqa_b200_decode_ex (bit mask; 0 = all three) */
+/* phases of gqa_b200_decode_ex: 0 = the default path (one launch when the batch
+ * allows it); a bit mask selects launches of the three-launch path, 7 = all three */
 #define GQA_B200_PHASE_PLAN 1
 #define GQA_B200_PHASE_DECODE 2
 #define GQA_B200_PHASE_MERGE 4
@@ -134,10 +153,12 @@ GQA_B200_API int gqa_b200_decode(const void* q, const void* k_cache, const void*
  *   chunk_tokens  base KV-chunk length (0 = built-in; otherwise 16..65536)
  *   kernel        GQA_B200_KERNEL_*
  *   max_ctas      cap on the persistent grid (0 = SM count x resident CTAs)
- *   phases        which of the three launches to enqueue (GQA_B200_PHASE_*;
- *                 0 = all).  A benchmark uses it to put its own events around
- *                 the decode kernel; the phases of one call must still run in
- *                 order plan, decode, merge on the same workspace.            */
+ *   phases        0 = default; otherwise which launches of the three-launch
+ *                 path to enqueue (GQA_B200_PHASE_*).  A benchmark uses it to put
+ *                 its own events around the decode kernel; the phases of one call
+ *                 must still run in order plan, decode, merge on the same
+ *                 workspace.  The three-launch path gives the same bits as the
+ *                 one-launch path for the same chunk_tokens.                    */
 GQA_B200_API int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
                                     const int32_t* block_table, const int32_t* context_lens,
                                     void* out, int dtype, int batch, int q_heads, int kv_heads,
@@ -162,7 +183,7 @@ GQA_B200_API int gqa_b200_decode_ex(const void* q, const void* k_cache, const vo
  * every GPU that loads the library holds that much until the process exits.
  *
  * The call allocates and frees nothing (no cudaMalloc/cudaFree, no allocating
- * library routine) and runs the same three kernels as gqa_b200_decode, so the
+ * library routine) and runs the same kernel as gqa_b200_decode, so the
  * result is identical.  Limits and rules:
  *   - a shape whose gqa_b200_workspace_bytes(..., chunk_tokens = 0) exceeds
  *     GQA_B200_STATIC_SCRATCH_BYTES is refused with GQA_B200_ERR_STATIC_LIMIT
@@ -172,8 +193,9 @@ GQA_B200_API int gqa_b200_decode_ex(const void* q, const void* k_cache, const vo
  *     (cudaGetSymbolAddress, with that device current); make that first call
  *     outside any stream capture;
  *   - all calls on a device share the one array, which keeps whatever the last
- *     call left in it.  Nothing in it has to be cleared by the caller (the plan
- *     kernel rewrites the header, work counter included, every call), but two
+ *     call left in it.  Nothing in it has to be cleared by the caller (the array
+ *     is zero when the library is loaded and every call puts its control words
+ *     back to zero), but two
  *     calls that may run at the same time on the GPU -- different streams, or
  *     different host threads -- race on it: serialise them, or give the
  *     concurrent ones gqa_b200_decode with workspaces of their own. */

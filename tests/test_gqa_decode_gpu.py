@@ -9,7 +9,7 @@ from conftest import TOL, full_cases, load_full, load_seeded, seed_cases
 from oracle import gqa_oracle
 
 import attention_b200 as attn
-from attention_b200 import synth
+from attention_b200 import _cabi, synth
 
 pytestmark = pytest.mark.gpu
 
@@ -156,12 +156,17 @@ def test_out_and_workspace_arguments():
     want = _oracle(*args)
     out = torch.full_like(args[0], float("nan"))
     need = attn.workspace_bytes(3, 8, 2, 128, 16, table.shape[1], 64)
-    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    ws = torch.zeros(need, dtype=torch.uint8, device=DEV)      # control words start at zero
     res = attn.gqa_decode(*args, out=out, workspace=ws, chunk_tokens=64)
     assert res is out
     _assert_close(out, want, torch.bfloat16)
-    hdr = ws[:12].view(torch.int32).cpu()
+    hdr = ws[:20].view(torch.int32).cpu()
     assert int(hdr[2]) == 0 and int(hdr[1]) == sum(-(-n // 64) for n in (300, 40, 1000))
+    assert int(hdr[0]) == 0 and int(hdr[4]) == 0               # counters back at zero
+    # the three-launch path on the same workspace, and the one-launch path after it
+    out3 = attn.gqa_decode(*args, workspace=ws, chunk_tokens=64, phases=7)
+    assert torch.equal(out3, out)
+    assert torch.equal(attn.gqa_decode(*args, workspace=ws, chunk_tokens=64), out)
     small = torch.empty(need - 256, dtype=torch.uint8, device=DEV)
     with pytest.raises(RuntimeError, match="workspace"):
         attn.gqa_decode(*args, workspace=small, chunk_tokens=64)
@@ -340,14 +345,84 @@ def test_randomized_shapes_against_oracle():
                       f"chunk={chunk} {kernel}")
 
 
+# --------------------------------------------------------------------------- one launch vs three
+@pytest.mark.parametrize("kernel", ["auto", "simt"])
+@pytest.mark.parametrize("chunk", [0, 16, 64, 512])
+def test_one_launch_and_three_launch_paths_agree(kernel, chunk):
+    """Same chunk list, same partial slots, same merge arithmetic: with an explicit chunk length
+    the two paths give identical bits; with the automatic one (the two paths may pick different
+    bases) they agree within the tolerance."""
+    lengths = [0, 1, 15, 16, 17, 300, 0, 1000, 64, 2500, 33, 4097, 5]
+    for dtype, hq, hkv in ((torch.bfloat16, 32, 8), (torch.float16, 28, 4), (torch.float32, 8, 2)):
+        q, k, v, table, lens = _make_case(lengths, hq, hkv, 128, 16, dtype, seed=chunk + hq)
+        args = _cuda(q, k, v, table, lens)
+        one = attn.gqa_decode(*args, kernel=kernel, chunk_tokens=chunk)
+        three = attn.gqa_decode(*args, kernel=kernel, chunk_tokens=chunk, phases=7)
+        if chunk:
+            assert torch.equal(one, three), f"{dtype} {kernel} chunk={chunk}"
+        _assert_close(one, three, dtype)
+        _assert_close(one, _oracle(*args), dtype, f"{dtype} {kernel} chunk={chunk}")
+        assert torch.count_nonzero(one[0]) == 0 and torch.count_nonzero(one[6]) == 0
+
+
+def test_one_launch_path_leaves_the_workspace_clean():
+    """After any call the work counter, the exit counter and every ticket are zero again, so the
+    next call (other lengths, other shape) can use the same workspace without clearing it."""
+    lib_need = attn.workspace_bytes(6, 32, 8, 128, 16, 400, 0)
+    ws = torch.zeros(lib_need, dtype=torch.uint8, device=DEV)
+    control = int(_cabi.load().gqa_b200_workspace_control_bytes())   # header + tickets
+    for seed, lengths in enumerate(([3000, 70, 0, 6000, 1, 999], [16, 16, 16, 16, 16, 16],
+                                    [6400, 6400, 6400, 1, 0, 0])):
+        q, k, v, table, lens = _make_case(lengths, 32, 8, 128, 16, torch.bfloat16, seed=seed)
+        wide = torch.full((6, 400), -1, dtype=torch.int32)
+        wide[:, : table.shape[1]] = table
+        args = _cuda(q, k, v, wide, lens)
+        for chunk in (0, 64):
+            if attn.workspace_bytes(6, 32, 8, 128, 16, 400, chunk) > lib_need:
+                continue
+            got = attn.gqa_decode(*args, workspace=ws, chunk_tokens=chunk)
+            _assert_close(got, _oracle(*args), torch.bfloat16, f"{lengths} chunk={chunk}")
+            words = ws[:control].view(torch.int32).cpu()
+            assert int(words[0]) == 0 and int(words[4]) == 0, "counters not released"
+            assert int(words[64:].abs().sum()) == 0, "a ticket was left behind"
+
+
+def test_calls_of_different_shapes_share_one_workspace():
+    """The control words sit at a fixed place, so the partials a small-shape call writes can
+    never be what a later, larger call reads as its arrival counters."""
+    big = attn.workspace_bytes(40, 128, 8, 256, 16, 100, 0)
+    ws = torch.zeros(big, dtype=torch.uint8, device=DEV)
+    shapes = [(3, 8, 2, 128, torch.bfloat16), (40, 128, 8, 256, torch.float32),
+              (7, 28, 4, 128, torch.float16), (40, 128, 8, 256, torch.float32)]
+    gen = torch.Generator().manual_seed(3)
+    for i, (batch, hq, hkv, d, dtype) in enumerate(shapes):
+        lengths = torch.randint(1, 1500, (batch,), generator=gen).tolist()
+        q, k, v, table, lens = _make_case(lengths, hq, hkv, d, 16, dtype, seed=i)
+        args = _cuda(q, k, v, table, lens)
+        for kernel in ("auto", "simt"):
+            got = attn.gqa_decode(*args, workspace=ws, kernel=kernel)
+            _assert_close(got, _oracle(*args), dtype, f"shape {i} {kernel}")
+
+
+def test_batches_beyond_the_one_launch_limit_take_three_launches():
+    """More than 2048 sequences: the prefix array no longer fits the decode CTA's shared memory,
+    the call falls back to plan + decode + merge."""
+    gen = torch.Generator().manual_seed(11)
+    lengths = torch.randint(0, 90, (2100,), generator=gen).tolist()
+    q, k, v, table, lens = _make_case(lengths, 8, 2, 64, 16, torch.float16, seed=12)
+    args = _cuda(q, k, v, table, lens)
+    _assert_close(attn.gqa_decode(*args), _oracle(*args), torch.float16)
+
+
 # --------------------------------------------------------------------------- stream capture
 def test_decode_can_be_captured_in_a_cuda_graph_and_replayed():
     """No allocation, no host read of the lengths, no synchronisation inside the call: the
-    three launches can be recorded once and replayed on new contents of the same buffers."""
+    launch can be recorded once and replayed on new contents of the same buffers (every run
+    leaves the workspace's control words at zero for the next)."""
     q, k, v, table, lens = _make_case([900, 40, 2500, 0, 64], 32, 8, 128, 16, torch.bfloat16, seed=21)
     dq, dk, dv, dt, dl = _cuda(q, k, v, table, lens)
     out = torch.empty_like(dq)
-    ws = torch.empty(attn.workspace_bytes(5, 32, 8, 128, 16, table.shape[1]), dtype=torch.uint8,
+    ws = torch.zeros(attn.workspace_bytes(5, 32, 8, 128, 16, table.shape[1]), dtype=torch.uint8,
                      device=DEV)
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):

@@ -26,7 +26,7 @@ def test_library_loads_and_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), name
     assert set(names) == set(_cabi.SIGNATURES), "ctypes table and header disagree"
-    assert lib.gqa_b200_abi_version() == 1
+    assert lib.gqa_b200_abi_version() == 2
     assert attn.is_cuda_extension_loaded()
 
 

@@ -39,6 +39,9 @@ def _decode_with_caller_workspace(lib, q, k, v, table, lens):
                                         table.size(1), 0)
     ws = torch.empty(need, dtype=torch.uint8, device=DEV)
     stream = torch.cuda.current_stream().cuda_stream
+    # a fresh workspace: its control words are zeroed once, through the C ABI
+    rc = lib.gqa_b200_workspace_init(ws.data_ptr(), ws.numel(), stream)
+    assert rc == 0, _cabi.strerror(rc)
     rc = lib.gqa_b200_decode(*_args(q, k, v, table, lens, out), ws.data_ptr(), ws.numel(), stream)
     assert rc == 0, _cabi.strerror(rc)
     return out
