@@ -60,9 +60,11 @@ inline int max_chunks_for_capacity(long long cap, int base) {
 // ---------------------------------------------------------------------------
 // kModePlanned   plan kernel -> decode kernel -> merge kernel (three launches)
 // kModeRefSplits caller-chosen split count, the reference's partial layout
-// kModeFused     ONE launch: every decode CTA derives the chunk list from context_lens
-//                itself, and the CTA that finishes the last chunk of a (sequence, kv head,
-//                head group) folds that group's partials into `out`
+// kModeFused     no plan launch: every decode CTA derives the chunk list from context_lens
+//                itself.  With fused_merge the decode kernel also merges (one launch in all):
+//                the CTA that takes the last ticket of a (sequence, kv head, head group)
+//                folds that group's partials into `out`; without it the merge kernel
+//                follows as a second launch.
 enum : int { kModePlanned = 0, kModeRefSplits = 1, kModeFused = 2 };
 
 struct DecodeParams {
@@ -85,6 +87,7 @@ struct DecodeParams {
     float* ref_partials;    // [batch, q_heads, splits, head_dim + 2]
     int splits;
     int mode;
+    int fused_merge;        // kModeFused: 1 = tickets and merge inside the decode kernel
     // shapes
     int batch, q_heads, kv_heads, group, head_dim;
     int heads_per_item;     // query heads of one kv head handled by one work item

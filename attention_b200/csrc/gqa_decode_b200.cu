@@ -268,11 +268,11 @@ cudaError_t launch_kernel(KernelT kernel, dim3 grid, int threads, size_t smem, c
     return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
-// Shared memory of the one-launch mode's [batch + 1] prefix array, in steps of 1 KB so that
+// Shared memory of the one-launch mode's chunk prefix and length arrays, in steps of 1 KB so that
 // the occupancy cache sees few distinct sizes.
 inline size_t fused_prefix_bytes(const DecodeParams& p) {
     if (p.mode != kModeFused) return 0;
-    return align_up(((size_t)p.batch + 1) * sizeof(int), 1024);
+    return align_up((2 * (size_t)p.batch + 1) * sizeof(int), 1024);   // chunk prefix + lengths
 }
 
 template <typename KernelT>
@@ -538,12 +538,37 @@ int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
     if (kernel == GQA_B200_KERNEL_SIMT) use_mma = false;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    constexpr int kSelfPlanPhases = GQA_B200_PHASE_ONE_LAUNCH | GQA_B200_PHASE_TWO_LAUNCH | GQA_B200_PHASE_SELF_DECODE;
+    if ((phases & kSelfPlanPhases) && phases != GQA_B200_PHASE_ONE_LAUNCH &&
+        phases != GQA_B200_PHASE_TWO_LAUNCH && phases != GQA_B200_PHASE_SELF_DECODE)
+        return GQA_B200_ERR_KERNEL;
     // (the SIMT kernel's groups of four query heads are the finest grouping any kernel uses)
     const long long ticket_count = (long long)batch * kv_heads * ((q_heads / kv_heads + 3) / 4);
-    if (phases == 0 && batch <= kFusedMaxBatch && ticket_count <= kFusedMaxTickets) {
-        // one launch: the decode kernel plans for itself and the last chunk of a sequence merges
+    const bool can_self_plan = batch <= kFusedMaxBatch;
+    const bool can_ticket = can_self_plan && ticket_count <= kFusedMaxTickets;
+    if ((phases == GQA_B200_PHASE_ONE_LAUNCH && !can_ticket) ||
+        ((phases == GQA_B200_PHASE_TWO_LAUNCH || phases == GQA_B200_PHASE_SELF_DECODE) && !can_self_plan))
+        return GQA_B200_ERR_KERNEL;
+    if ((phases == 0 && can_self_plan) || (phases & kSelfPlanPhases)) {
+        // No plan launch: the decode kernel cuts the sequences itself.  Whether it also merges is
+        // decided from the static shape: tickets cost a CTA a fence and an atomic round trip per
+        // item and put the merge of the last sequences behind the streaming, which only pays
+        // when every work item can have a CTA of its own even at the finest chunk length, i.e.
+        // on small batches of short tables.  Otherwise the merge kernel follows.
+        const int hpi = use_mma ? 16 : simt_heads_per_item(head_dim, q_heads / kv_heads);
+        const long long head_groups = (q_heads / kv_heads + hpi - 1) / hpi;
+        const long long finest_items = (long long)batch *
+            max_chunks_for_capacity((long long)max_pages * block_size, base ? base : 1024 >> (kNumAutoBases - 1)) *
+            kv_heads * head_groups;
+        const bool one_launch = phases == GQA_B200_PHASE_ONE_LAUNCH ||
+                                (phases == 0 && can_ticket && finest_items <= kAssumedCtaSlots);
         p.mode = kModeFused;
-        return (int)launch_decode(p, dtype, use_mma, max_ctas, s);
+        p.fused_merge = one_launch ? 1 : 0;
+        cudaError_t e = launch_decode(p, dtype, use_mma, max_ctas, s);
+        if (e != cudaSuccess || one_launch || phases == GQA_B200_PHASE_SELF_DECODE) return (int)e;
+        DecodeParams pm = p;            // the merge kernels read the plan the decode kernel published
+        pm.mode = kModePlanned;
+        return (int)launch_merge(pm, dtype, s);
     }
     if (phases == 0) phases = GQA_B200_PHASE_PLAN | GQA_B200_PHASE_DECODE | GQA_B200_PHASE_MERGE;
     cudaError_t e = cudaSuccess;

@@ -154,7 +154,7 @@ gqa_decode_mma_kernel(const DecodeParams p) {
     int* s_table = reinterpret_cast<int*>(s_l + NWARPS * 16);           // [table_smem_entries]
     int* s_off = s_table + p.table_smem_entries;                         // fused mode: [batch + 1]
     __shared__ int s_item;
-    __shared__ int s_flag;
+    __shared__ FusedPending s_pending;
     __shared__ int s_red[2 * kNumAutoBases * 32 + 32];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -171,6 +171,7 @@ gqa_decode_mma_kernel(const DecodeParams p) {
     pdl_launch_dependents();
     pdl_wait();   // the plan kernel wrote hdr / items; the call before left the counters at zero
     const bool fused = p.mode == kModeFused;
+    const bool tickets = fused && p.fused_merge;   // merge inside this kernel
     const bool counted = p.mode != kModeRefSplits;      // items are pulled from the work counter
     FusedPlan plan;
     plan.base = p.chunk_base;
@@ -204,10 +205,7 @@ gqa_decode_mma_kernel(const DecodeParams p) {
     }
     int4 rec = make_int4(0, 0, 0, 0);
     if (!fused && item < n_items) rec = load_item_record(p, item);
-    // one-launch mode: the ticket of the item before (taken at its end, looked at one item later)
-    bool pend = false;
-    WorkItem pend_w{};
-    int pend_rows = 0, pend_old = 0;
+    int n_pend = 0;     // one-launch mode: multi-chunk items whose tickets are still to be taken
 
     while (item < n_items) {
         int next = 0;
@@ -473,22 +471,19 @@ gqa_decode_mma_kernel(const DecodeParams p) {
         } else {
             store_empty<T>(p, w, rows_valid);
         }
-        const bool multi = fused && nonempty && w.n_parts > 1;
-        if (multi) __threadfence();   // this thread's partial stores are visible device-wide ...
-        __syncthreads();   // ... for the whole CTA; rings, Q tile, table and s_item are free again
-        if (pend)
-            fused_resolve_ticket<T>(p, pend_w, pend_rows, pend_old, &s_flag, s_ring, NWARPS * G::kWarpBytes);
-        pend = multi;
-        if (multi) {
-            if (tid == 0) pend_old = atomicAdd(fused_ticket(p, w), 1);
-            pend_w = w;
-            pend_rows = rows_valid;
+        __syncthreads();   // rings, Q tile, table and s_item are free again
+        if (tickets && nonempty && w.n_parts > 1) {
+            if (tid == 0) fused_note_item(s_pending, n_pend, p, w);
+            if (++n_pend == kFusedMaxPending) {
+                fused_flush_tickets<T, true, true>(p, s_pending, n_pend, s_ring, NWARPS * G::kWarpBytes);
+                n_pend = 0;
+            }
         }
         item = nxt;
         rec = rec_next;
     }
-    if (pend) fused_resolve_ticket<T>(p, pend_w, pend_rows, pend_old, &s_flag, s_ring, NWARPS * G::kWarpBytes);
-    if (counted) decode_counters_release(p, plan.total_chunks, plan.base);
+    if (tickets) fused_flush_tickets<T, true, true>(p, s_pending, n_pend, s_ring, NWARPS * G::kWarpBytes);
+    if (counted) decode_counters_release(p);
 }
 
 }  // namespace gqa_b200

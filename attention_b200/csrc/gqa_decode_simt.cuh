@@ -66,7 +66,7 @@ gqa_decode_simt_kernel(const DecodeParams p) {
     int* s_table = reinterpret_cast<int*>(s_l + NW * GB);        // [table_smem_entries]
     int* s_off = s_table + p.table_smem_entries;                 // fused mode: [batch + 1]
     __shared__ int s_item;
-    __shared__ int s_flag;
+    __shared__ FusedPending s_pending;
     __shared__ int s_red[2 * kNumAutoBases * 32 + 32];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -76,6 +76,7 @@ gqa_decode_simt_kernel(const DecodeParams p) {
     pdl_launch_dependents();
     pdl_wait();   // the plan kernel wrote hdr / items; the call before left the counters at zero
     const bool fused = p.mode == kModeFused;
+    const bool tickets = fused && p.fused_merge;   // merge inside this kernel
     const bool counted = p.mode != kModeRefSplits;      // items are pulled from the work counter
     FusedPlan plan;
     plan.base = p.chunk_base;
@@ -89,6 +90,7 @@ gqa_decode_simt_kernel(const DecodeParams p) {
     }
     const long long row_elems = (long long)p.kv_heads * D;
 
+    int n_pend = 0;     // one-launch mode: multi-chunk items whose tickets are still to be taken
     int item;
     if (counted) {
         if (tid == 0) s_item = atomicAdd(p.hdr + kHdrCounter, 1);
@@ -224,9 +226,15 @@ gqa_decode_simt_kernel(const DecodeParams p) {
             __syncthreads();
             combine_and_store<T, NW, VEC4>(p, w, s_o, GB * o_stride, o_stride, s_m, s_l, GB,
                                            rows_valid);
-            if (fused && w.n_parts > 1) fused_finish_item<T, VEC4>(p, w, rows_valid, &s_flag);
         }
         __syncthreads();
+        if (tickets && w.t1 > w.t0 && w.n_parts > 1) {
+            if (tid == 0) fused_note_item(s_pending, n_pend, p, w);
+            if (++n_pend == kFusedMaxPending) {
+                fused_flush_tickets<T, VEC4, false>(p, s_pending, n_pend, nullptr, 0);
+                n_pend = 0;
+            }
+        }
         if (counted) {
             if (tid == 0) s_item = next;
             __syncthreads();
@@ -235,7 +243,8 @@ gqa_decode_simt_kernel(const DecodeParams p) {
             item = next;
         }
     }
-    if (counted) decode_counters_release(p, plan.total_chunks, plan.base);
+    if (tickets) fused_flush_tickets<T, VEC4, false>(p, s_pending, n_pend, nullptr, 0);
+    if (counted) decode_counters_release(p);
 }
 
 }  // namespace gqa_b200

@@ -7,10 +7,11 @@
 //   * every decode CTA derives the chunk list from context_lens itself (a block scan
 //     over at most kFusedMaxBatch sequences into shared memory) and turns an item
 //     number into (sequence, chunk) with a binary search;
-//   * the partial of a chunk goes to its slot as before; the CTA then takes a ticket of
-//     its (sequence, kv head, head group), and the CTA that draws the last ticket folds
-//     the partials IN SLOT ORDER, so the bits do not depend on which CTA came last.
-//     Nobody waits for anybody: there is no spin anywhere;
+//   * the partial of a chunk goes to its slot as before; when a CTA has run out of work it
+//     takes a ticket of the (sequence, kv head, head group) of every multi-chunk item it
+//     processed, and the CTA that draws a group's last ticket folds that group's partials
+//     IN SLOT ORDER, so the bits do not depend on which CTA came last.  Nobody waits for
+//     anybody: there is no spin anywhere;
 //   * the work counter, the exit counter and the tickets are left at zero by the kernel
 //     itself (the last arriver clears its ticket, the last CTA to leave clears the
 //     counters), so the control words of a workspace are zeroed once, before its first use.
@@ -21,6 +22,11 @@
 #include "gqa_common.cuh"
 
 namespace gqa_b200 {
+
+// Release / acquire fence at device scope (__threadfence() is the sequentially consistent one).
+__device__ __forceinline__ void fence_acq_rel_gpu() {
+    asm volatile("fence.acq_rel.gpu;" ::: "memory");
+}
 
 struct FusedPlan {
     int base;           // base chunk length in tokens
@@ -43,7 +49,7 @@ __device__ __forceinline__ int fused_chunks_for(int len, int base) {
 // the benchmark workloads at explicit bases 1024 .. 128 (group 4 to 8, bf16 / fp16, D 128):
 // halving the base costs about 0.5 us per extra item per CTA and shortens the tail by half
 // an item.
-constexpr float kFusedItemOverheadTokens = 56.f;
+constexpr float kFusedItemOverheadTokens = 64.f;
 constexpr float kFusedTailFraction = 0.5f;
 
 __device__ __forceinline__ int fused_pick_base(const int (&cnt)[kNumAutoBases], const int (&longest)[kNumAutoBases],
@@ -61,19 +67,21 @@ __device__ __forceinline__ int fused_pick_base(const int (&cnt)[kNumAutoBases], 
 }
 
 // All THREADS threads of the CTA.  Fills s_off[0 .. batch] with the exclusive prefix of
-// chunks per sequence and returns the plan.  s_red: scratch of 2 * kNumAutoBases * 32 + 32 ints.
+// chunks per sequence and s_off[batch + 1 + b] with the clamped length of sequence b (an item
+// is then set up from shared memory alone), and returns the plan.
+// s_red: scratch of 2 * kNumAutoBases * 32 + 32 ints.
 template <int THREADS>
 __device__ __forceinline__ FusedPlan fused_plan(const DecodeParams& p, int* s_off, int* s_red) {
+    int* s_len = s_off + p.batch + 1;
     constexpr int NW = THREADS / 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int base = p.chunk_base;
-    // clamped lengths into s_off (converted to the prefix below)
     int cnt[kNumAutoBases], longest[kNumAutoBases];
 #pragma unroll
     for (int i = 0; i < kNumAutoBases; ++i) { cnt[i] = 0; longest[i] = 0; }
     for (int b = tid; b < p.batch; b += THREADS) {
         const int len = clamp_len(p, b);
-        s_off[b] = len;
+        s_len[b] = len;
         if (base == 0) {
 #pragma unroll
             for (int i = 0; i < kNumAutoBases; ++i) {
@@ -110,13 +118,13 @@ __device__ __forceinline__ FusedPlan fused_plan(const DecodeParams& p, int* s_of
         }
         base = fused_pick_base(cnt, longest, p.kv_heads * p.head_groups, (int)gridDim.x, p.cap_chunks);
     }
-    __syncthreads();   // every length is in s_off; s_red is free again
+    __syncthreads();   // every length is in s_len; s_red is free again
 
     // exclusive prefix of chunks: each thread owns a contiguous run of sequences
     const int run = (p.batch + THREADS - 1) / THREADS;
     const int b0 = min(p.batch, tid * run), b1 = min(p.batch, b0 + run);
     int mine = 0;
-    for (int b = b0; b < b1; ++b) mine += fused_chunks_for(s_off[b], base);
+    for (int b = b0; b < b1; ++b) mine += fused_chunks_for(s_len[b], base);
     int incl = mine;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
@@ -135,12 +143,21 @@ __device__ __forceinline__ FusedPlan fused_plan(const DecodeParams& p, int* s_of
     }
     int at = before + incl - mine;
     for (int b = b0; b < b1; ++b) {
-        const int n = fused_chunks_for(s_off[b], base);
         s_off[b] = at;
-        at += n;
+        at += fused_chunks_for(s_len[b], base);
     }
     if (tid == 0) s_off[p.batch] = total;
     __syncthreads();
+    if (blockIdx.x == 0) {
+        // one CTA publishes the plan for the merge kernel that may follow (and for debugging);
+        // every CTA computes the same one
+        for (int b = tid; b <= p.batch; b += THREADS) p.chunk_off[b] = s_off[b];
+        if (tid == 0) {
+            p.hdr[kHdrTotalChunks] = total;
+            p.hdr[kHdrChunkBase] = base;
+            p.hdr[kHdrStatus] = total > p.cap_chunks ? 1 : 0;
+        }
+    }
     FusedPlan plan;
     plan.base = base;
     plan.total_chunks = total > p.cap_chunks ? p.cap_chunks : total;
@@ -162,7 +179,7 @@ __device__ __forceinline__ WorkItem fused_item(const DecodeParams& p, int item, 
         if (s_off[mid] <= cg) lo = mid; else hi = mid;
     }
     w.b = lo;
-    const int len = clamp_len(p, lo);
+    const int len = s_off[p.batch + 1 + lo];
     const int ct = chunk_tokens_for(len, base);
     w.part = cg - s_off[lo];
     const long long t0 = (long long)w.part * ct;
@@ -351,70 +368,77 @@ __device__ __forceinline__ void fused_merge_rows_staged(const DecodeParams& p, c
     }
 }
 
-__device__ __forceinline__ int32_t* fused_ticket(const DecodeParams& p, const WorkItem& w) {
-    return p.tickets + ((size_t)w.b * p.kv_heads + w.kvh) * p.head_groups + w.hg;
+// The ticket protocol.  A release fence followed by an atomic costs its thread, and through
+// the next CTA barrier the whole CTA, one to two microseconds: measured per multi-chunk item,
+// that was 5 % of a long-context call.  So tickets are not taken item by item.  A CTA keeps a
+// list (shared memory) of the multi-chunk items whose partial it has stored, and takes all
+// their tickets together when it has run out of work (or when the list is full): one barrier,
+// then one thread per list entry fences and takes that entry's ticket, in parallel.  For
+// every entry that turned out to be the last arrival the CTA then merges the sequence.
+// All CTAs run out of work at about the same time, so the merges of a call run side by side
+// on as many CTAs as there are (sequence, kv head) groups, after the streaming.
+constexpr int kFusedMaxPending = 32;
+
+struct FusedPending {
+    int4 rec[kFusedMaxPending];    // (sequence, kv head * head_groups + head group, partials, first slot)
+    int last[kFusedMaxPending];
+};
+
+// thread 0, after the item's closing barrier was passed by everyone
+__device__ __forceinline__ void fused_note_item(FusedPending& pd, int n, const DecodeParams& p, const WorkItem& w) {
+    pd.rec[n] = make_int4(w.b, w.kvh * p.head_groups + w.hg, w.n_parts, (int)(w.part_slot - w.part));
 }
 
-// Deferred form of the ticket protocol for a kernel that has more items to do: the atomic is
-// issued at the end of an item (after every thread's __threadfence and a CTA barrier) and its
-// result is only looked at one item later, so nobody idles for the round trip to L2.
-//   fused_take_ticket     thread 0 issues the atomic; returns the count before this arrival
-//   fused_resolve_ticket  all threads, later: if the arrival was the last one, merge
-template <typename T>
-__device__ __forceinline__ void fused_resolve_ticket(const DecodeParams& p, const WorkItem& w, int rows_valid,
-                                                     int old, int* s_flag, unsigned char* smem, int smem_bytes) {
-    if (threadIdx.x == 0) {
-        const int last = old == w.n_parts - 1;
-        if (last) *fused_ticket(p, w) = 0;             // nobody else comes to this ticket in this call
-        *s_flag = last;
-    }
-    __syncthreads();
-    if (*s_flag) {
-        __threadfence();                               // the other CTAs' partials, published before their tickets
-        if (fused_merge_fits_smem(p, w.n_parts, rows_valid, (int)blockDim.x, smem_bytes))
-            fused_merge_rows_staged<T>(p, w, rows_valid, smem, smem_bytes);
-        else
-            fused_merge_rows<T, true>(p, w, rows_valid);
-    }
-    __syncthreads();                                   // s_flag and the staging memory are free again
-}
-
-// After every thread of the CTA has stored its share of the item's partial: take the
-// ticket; the CTA that holds the last one merges.  s_flag: one int of shared memory.
-template <typename T, bool VEC4>
-__device__ __forceinline__ void fused_finish_item(const DecodeParams& p, const WorkItem& w, int rows_valid,
-                                                  int* s_flag) {
-    __threadfence();                    // this thread's partial stores are visible device-wide ...
-    __syncthreads();                    // ... for every thread of the CTA, before the ticket is taken
-    if (threadIdx.x == 0) {
-        int32_t* t = p.tickets + ((size_t)w.b * p.kv_heads + w.kvh) * p.head_groups + w.hg;
+// All threads of the CTA.  STAGED: merge through `smem` (free shared memory, 16-byte aligned).
+template <typename T, bool VEC4, bool STAGED>
+__device__ __forceinline__ void fused_flush_tickets(const DecodeParams& p, FusedPending& pd, int n_pend,
+                                                    unsigned char* smem, int smem_bytes) {
+    if (n_pend == 0) return;
+    __syncthreads();                    // the list is written; every partial of its items was stored
+                                        // before an earlier barrier
+    if ((int)threadIdx.x < n_pend) {
+        const int4 r = pd.rec[threadIdx.x];
+        int32_t* t = p.tickets + ((size_t)r.x * p.kv_heads * p.head_groups + r.y);
+        fence_acq_rel_gpu();            // release: cumulative over what the barriers showed this thread
         const int old = atomicAdd(t, 1);
-        const int last = old == w.n_parts - 1;
+        const int last = old == r.z - 1;
         if (last) *t = 0;               // nobody else comes to this ticket in this call
-        *s_flag = last;
+        pd.last[threadIdx.x] = last;
     }
     __syncthreads();
-    if (*s_flag) {
-        __threadfence();                // the other CTAs' partials, published before their tickets
+    for (int i = 0; i < n_pend; ++i) {
+        if (!pd.last[i]) continue;      // (uniform: shared memory)
+        const int4 r = pd.rec[i];
+        WorkItem w;
+        w.b = r.x;
+        w.kvh = r.y / p.head_groups;
+        w.hg = r.y - w.kvh * p.head_groups;
+        w.n_parts = r.z;
+        w.part = 0;
+        w.part_slot = r.w;
+        w.t0 = w.t1 = 0;
+        const int rows_valid = min(p.heads_per_item, p.group - w.hg * p.heads_per_item);
+        fence_acq_rel_gpu();            // acquire: the other CTAs' partials, published before their tickets
+        if constexpr (STAGED) {
+            if (fused_merge_fits_smem(p, w.n_parts, rows_valid, (int)blockDim.x, smem_bytes)) {
+                fused_merge_rows_staged<T>(p, w, rows_valid, smem, smem_bytes);
+                continue;
+            }
+        }
         fused_merge_rows<T, VEC4>(p, w, rows_valid);
     }
+    __syncthreads();                    // the list and the staging memory are free again
 }
 
 // Last statement of a decode kernel that pulled items from the work counter: the CTA that
-// leaves last puts the counters back to zero (and records the plan in the debug words).
-__device__ __forceinline__ void decode_counters_release(const DecodeParams& p, int total_chunks, int base) {
+// leaves last puts the counters back to zero.
+__device__ __forceinline__ void decode_counters_release(const DecodeParams& p) {
     if (threadIdx.x != 0) return;
-    __threadfence();
+    fence_acq_rel_gpu();
     const int old = atomicAdd(p.hdr + kHdrDone, 1);
     if (old == (int)gridDim.x - 1) {
         p.hdr[kHdrCounter] = 0;
         p.hdr[kHdrDone] = 0;
-        if (p.mode == kModeFused) {
-            p.hdr[kHdrTotalChunks] = total_chunks;
-            p.hdr[kHdrChunkBase] = base;
-            p.hdr[kHdrStatus] = 0;
-        }
-        __threadfence();
     }
 }
 

@@ -188,24 +188,43 @@ __global__ void __launch_bounds__(kMergeWarps * 32) gqa_merge_kernel(const Decod
 #pragma unroll
         for (int j = 0; j < (VEC4 ? 4 : 1); ++j) acc[i][j] = 0.f;
     float sum = 0.f;
-    for (int c = warp; c < n_parts; c += kMergeWarps) {
-        const float lw = part_l(c);
-        if (!(lw > 0.f)) continue;
-        const float wgt = fast_exp2(part_m(c) - mx);
-        sum += wgt * lw;
-        const float* src = part_acc(c);
+    // The warp's partitions are fetched four at a time: all loads of a batch are issued before
+    // the first is used (a long sequence has up to 64 partitions; one dependent round trip per
+    // partition is what the kernel's duration used to consist of).  The additions stay in
+    // partition order.
+    constexpr int kBatch = 4;
+    for (int cb = warp; cb < n_parts; cb += kMergeWarps * kBatch) {
+        float lw[kBatch], mw[kBatch];
+        float x[kBatch][kCols][VEC4 ? 4 : 1];
 #pragma unroll
-        for (int i = 0; i < kCols; ++i) {
-            if (VEC4) {
-                const int col = (i * 32 + lane) * 4;
-                if (col < D) {
-                    const float4 x = *reinterpret_cast<const float4*>(src + col);
-                    acc[i][0] += wgt * x.x; acc[i][1] += wgt * x.y;
-                    acc[i][2] += wgt * x.z; acc[i][3] += wgt * x.w;
+        for (int u = 0; u < kBatch; ++u) {
+            const int c = cb + u * kMergeWarps;
+            const bool live = c < n_parts;
+            lw[u] = live ? part_l(c) : 0.f;
+            mw[u] = live ? part_m(c) : -INFINITY;
+            const float* src = part_acc(live ? c : 0);
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) {
+                if constexpr (VEC4) {
+                    const int col = (i * 32 + lane) * 4;
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (live && col < D) v = *reinterpret_cast<const float4*>(src + col);
+                    x[u][i][0] = v.x; x[u][i][1] = v.y; x[u][i][2] = v.z; x[u][i][3] = v.w;
+                } else {
+                    const int col = i * 32 + lane;
+                    x[u][i][0] = (live && col < D) ? src[col] : 0.f;
                 }
-            } else {
-                const int col = i * 32 + lane;
-                if (col < D) acc[i][0] += wgt * src[col];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            if (!(lw[u] > 0.f)) continue;
+            const float wgt = fast_exp2(mw[u] - mx);
+            sum += wgt * lw[u];
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) {
+#pragma unroll
+                for (int j = 0; j < (VEC4 ? 4 : 1); ++j) acc[i][j] += wgt * x[u][i][j];
             }
         }
     }

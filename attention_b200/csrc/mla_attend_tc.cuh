@@ -35,8 +35,12 @@
 //   warps 8-9    loaders: 16-byte cp.async of this CTA's blocks of each cache row, one page lookup
 //                per 32 tokens when the page size is a multiple of 32 tokens, else one per row
 //   warp 10      one lane issues every tcgen05.mma
-// There is no CTA-wide barrier in the token loop; the hand-offs are mbarriers (and one 64-thread
-// named barrier between the two warps that share a TMEM lane quadrant).  Every mbarrier wait is
+// There is no CTA-wide barrier in the token loop, and none between work items either: the
+// mbarriers are initialised once per kernel and their phases run on across the items of a CTA
+// pair (every tile the pair processes has a running number J, and stage, buffer and parity of
+// every hand-off derive from J), so the loader warps run ahead into the next item's tiles while
+// the softmax warps still store the current item's rows.  The hand-offs are mbarriers (and one
+// 64-thread named barrier between the two warps that share a TMEM lane quadrant).  Every mbarrier wait is
 // time-bounded: a wait that runs out marks the CTA dead and raises the status word, and the CTA
 // still walks the protocol to the end, so its peer is never left waiting and no CTA exits
 // while the other may still write into its memory.
@@ -73,12 +77,13 @@ struct MlaTcGeom {
     static constexpr int kBlocks = 5;                                   // 128-byte column blocks (rank 1)
     static constexpr int kTileBlockBytes = kMlaTcBN * 128;              // 8 KB: one tile's rows of one block
     static constexpr int kStageBytes = kBlocks * kTileBlockBytes;       // 40 KB: [block][64 rows][128 B]
-    static constexpr int kQRopeBytes = kMlaTcRows * 128;                // 16 KB: rotated query block (rank 1)
+    static constexpr int kQRopeBytes = kMlaTcRows * 128;                // 16 KB: rotated query block (rank 1),
+                                                                        // two of them (work items alternate)
     static constexpr int kXBytes = kMlaTcRows * kMlaTcBN * 4;           // 32 KB, two of them
     static constexpr int kOffK = 0;
     static constexpr int kOffQr = kOffK + kMlaTcStages * kStageBytes;
-    static constexpr int kOffX = kOffQr + kQRopeBytes;
-    static constexpr int kSmemBytes = kOffX + 2 * kXBytes;              // 204800
+    static constexpr int kOffX = kOffQr + 2 * kQRopeBytes;
+    static constexpr int kSmemBytes = kOffX + 2 * kXBytes;              // 221184
     // tensor memory columns
     static constexpr int kColS = 0;                                     // kMlaTcSBufs x 64
     static constexpr int kColO = kMlaTcSBufs * kMlaTcBN;                // 256
@@ -273,6 +278,13 @@ mla_tc_merge_kernel(const MlaParams p) {
     }
 }
 
+#ifdef MLA_TC_STAMPS
+__device__ unsigned long long g_mla_stamps[160 * 64];
+#define MLA_STAMP(k) do { if (tid == 0 && (k) < 64) g_mla_stamps[blockIdx.x * 64 + (k)] = tc::global_timer_ns(); } while (0)
+#else
+#define MLA_STAMP(k) do {} while (0)
+#endif
+
 // grid (2 * pairs), cluster (2, 1, 1): persistent pairs that walk the schedule written by
 // mla_tc_plan_kernel (p.tc_sched).  p.page_shift = log2(page) or -1.
 template <typename T>
@@ -290,6 +302,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     __shared__ uint32_t s_tmem;
     __shared__ int s_dead;
     __shared__ float s_max[2][2][kMlaTcRows];        // [tile parity][column half][row]: half-row maxima
+    __shared__ float s_half[2][kMlaTcRows];          // [column half][row]: half-row sums at the end of an item
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool is_loader = tid >= NT && tid < NT + NL, is_mma = tid >= NT + NL;
@@ -303,6 +316,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
 
     pdl_launch_dependents();
     pdl_wait();                                      // the schedule and the queries come from earlier kernels
+    MLA_STAMP(0);
     const uint32_t s_base = tc::smem_u32(smem);
     if (s_base & 1023u) {                            // the swizzled tiles need a 1024-byte aligned base
         if (tid == 0 && status) atomicExch(status, 3);
@@ -332,7 +346,42 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     const int* sched = p.tc_sched;
     const int total_tiles = sched[0], per_range = sched[1], n_ranges = sched[2];
     const int* prefix = sched + 4;                   // prefix[u] = tiles before unit u, [units + 1]
-    bool first_item = true;
+    // tiles this pair will process over all of its ranges: they are numbered J = 0, 1, ... in the
+    // order they are processed, across work items
+    int pair_tiles = 0;
+    for (int range = blockIdx.x >> 1; range < n_ranges; range += gridDim.x >> 1)
+        pair_tiles += min(total_tiles, (range + 1) * per_range) - range * per_range;
+    // With few heads most of the 128 rows are padding.  A softmax warp whose 32 rows hold no
+    // query row in ANY unit of this launch takes no part at all (its rows of Q, S, P and O are
+    // never read by anyone); the barrier counts and the bytes expected from the peer cover the
+    // live warps only.  (The host passes 4 when units differ in their number of rows.)
+    const int live_quads = p.tc_live_quads;
+    const int live_warps = 2 * live_quads;
+    const uint32_t x_bytes = (uint32_t)live_warps * 32u * (uint32_t)(kMlaTcBN / 2) * 4u;
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < NS; ++i) { tc::mbar_init(bar_full + i * 8, NL); tc::mbar_init(bar_empty + i * 8, 1); }
+#pragma unroll
+        for (int i = 0; i < NSB; ++i) tc::mbar_init(bar_s0 + i * 8, 1);
+        tc::mbar_init(bar_p, live_warps);            // one arrival per live softmax warp
+        tc::mbar_init(bar_q, live_warps);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            tc::mbar_init(bar_x + i * 8, 1);         // one local arrival announcing the bytes per tile
+            tc::mbar_init(bar_free + i * 8, live_warps);   // one arrival per live softmax warp of the peer
+        }
+        tc::fence_mbar_init();
+        if (pair_tiles > 0) tc::mbar_arrive_expect_tx(bar_x, x_bytes);         // tile 0
+        if (pair_tiles > 1) tc::mbar_arrive_expect_tx(bar_x + 8, x_bytes);     // tile 1
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::cluster_sync_all();                          // both CTAs' barriers exist before any remote arrival
+    tc::tc_fence_after();
+    MLA_STAMP(1);
+    bool alive = true;
+    int J0 = 0;                                      // running number of the item's first tile
+    int item_no = 0;                                 // items of this pair so far
     for (int range = blockIdx.x >> 1; range < n_ranges; range += gridDim.x >> 1) {
     int pos = range * per_range;
     const int range_end = min(total_tiles, pos + per_range);
@@ -362,40 +411,8 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     const int t0 = seg_lo * BN;
     const int t1 = min(end_max, seg_hi * BN);
     const int n_tiles = seg_hi - seg_lo;
-    // With few heads most of the 128 rows are padding.  A softmax warp whose 32 rows hold no
-    // query row takes no part in the item (its rows of Q, S, P and O are never read by anyone);
-    // the barrier counts and the bytes expected from the peer cover the live warps only.
-    const int live_quads = min(4, (min(R - g0, BM) + 31) / 32);
-    const int live_warps = 2 * live_quads;
-    const uint32_t x_bytes = (uint32_t)live_warps * 32u * (uint32_t)(kMlaTcBN / 2) * 4u;
     const long long grow = (long long)b * R + g;     // global query row (softmax threads)
-
-    if (tid == 0) {
-        if (!first_item) {
-#pragma unroll
-            for (int i = 0; i < 2 * NS + NSB + 6; ++i) tc::mbar_inval(bar_full + i * 8);
-        }
-#pragma unroll
-        for (int i = 0; i < NS; ++i) { tc::mbar_init(bar_full + i * 8, NL); tc::mbar_init(bar_empty + i * 8, 1); }
-#pragma unroll
-        for (int i = 0; i < NSB; ++i) tc::mbar_init(bar_s0 + i * 8, 1);
-        tc::mbar_init(bar_p, live_warps);            // one arrival per live softmax warp
-        tc::mbar_init(bar_q, live_warps);
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            tc::mbar_init(bar_x + i * 8, 1);         // one local arrival announcing the bytes per tile
-            tc::mbar_init(bar_free + i * 8, live_warps);   // one arrival per live softmax warp of the peer
-        }
-        tc::fence_mbar_init();
-        tc::mbar_arrive_expect_tx(bar_x, x_bytes);                             // tile 0
-        if (n_tiles > 1) tc::mbar_arrive_expect_tx(bar_x + 8, x_bytes);        // tile 1
-    }
-    first_item = false;
-    tc::tc_fence_before();
-    __syncthreads();
-    tc::cluster_sync_all();                          // both CTAs' barriers exist before any remote arrival
-    tc::tc_fence_after();
-    bool alive = true;
+    const uint32_t sqr_i = sqr + (uint32_t)(item_no & 1) * G::kQRopeBytes;   // this item's rotated block of Q_r
 
     auto timed_out = [&]() {
         s_dead = 1;
@@ -413,13 +430,19 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         // =============================== loader warps ===============================
         const int lt = tid - NT;
         const int cpr = nb * 8;                      // 16-byte chunks of a row that this CTA owns
-        if (rank) {   // the rotated block of Q_r stays in shared memory: [128 rows][128 B], rides on full[0]
+        if (rank) {   // the rotated block of Q_r stays in shared memory: [128 rows][128 B]; it rides
+                      // on the full barrier of the item's first tile
+            // The buffer was last used by the item before the previous one, whose tiles are all
+            // numbered J0 - 2 or lower: once the scores of tile J0 - 2 are done (the tensor pipe
+            // runs in order), nothing reads it any more.  That phase of bar_s cannot be
+            // overtaken: its successor needs tile J0, which is loaded below.
+            if (item_no >= 2) wait_bar(bar_s0 + ((J0 - 2) % NSB) * 8, ((J0 - 2) / NSB) & 1);
             const T* qr = reinterpret_cast<const T*>(p.qr);
             for (int i = lt; i < BM * 8; i += NL) {
                 const int row = i >> 3, c = i & 7;
                 const bool valid = g0 + row < R;
                 const T* src = qr + ((long long)b * R + (valid ? g0 + row : 0)) * kMlaTcDr + c * 8;
-                cp_async16<0>(sqr + row * 128 + ((c ^ (row & 7)) << 4), src, valid ? 16 : 0, 0);
+                cp_async16<0>(sqr_i + row * 128 + ((c ^ (row & 7)) << 4), src, valid ? 16 : 0, 0);
             }
         }
         // this thread's chunks of a 32-row half tile: the same (row, 16-byte column) for every
@@ -440,8 +463,9 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         const int last_block = (int)(p.num_blocks - 1);
         const bool page_run = p.page_shift >= 5;     // a 32-token half never straddles a page
         for (int j = 0; j < n_tiles; ++j) {
-            const int stage = j % NS;
-            if (j >= NS) wait_bar(bar_empty + stage * 8, ((j / NS) - 1) & 1);
+            const int J = J0 + j;
+            const int stage = J % NS;
+            if (J >= NS) wait_bar(bar_empty + stage * 8, ((J / NS) - 1) & 1);
 #pragma unroll
             for (int half = 0; half < BN / HR; ++half) {
                 const uint32_t st = sk + stage * G::kStageBytes + half * (HR * 128);
@@ -480,7 +504,6 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             }
             tc::cp_async_arrive(bar_full + stage * 8);
         }
-        cp_async_wait<0>();
     } else if (is_mma) {
         // =============================== MMA warp: one lane issues everything ===============================
         if (lane == 0) {
@@ -490,15 +513,16 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             // no carry out of it below 256 KB), so each one is a base plus a small offset: the
             // issuing lane's instruction stream per MMA stays a handful of instructions.
             const uint64_t dk0 = tc::smem_desc_sw128_kmajor(sk);
-            const uint64_t dqr0 = tc::smem_desc_sw128_kmajor(sqr);
+            const uint64_t dqr0 = tc::smem_desc_sw128_kmajor(sqr_i);
             const uint64_t dv0 = tc::smem_desc_sw128_mnmajor(sk, G::kTileBlockBytes);
             // S_r(j) = Q_r C_r(j)^T into score buffer j & 1.  A = the latent part of Q_r from tensor
             // memory (8 columns = 16 elements per step) and, on rank 1, its rotated block from
             // shared memory.  (An MMA costs the issuing lane about 70 cycles whatever its width,
             // which is why the tile is 64 tokens wide and not 32.)
             auto issue_qk = [&](int j) {
-                const uint64_t dk = dk0 + (uint64_t)(((j % NS) * G::kStageBytes) >> 4);
-                const uint32_t d = tmem + (j % NSB) * BN;
+                const int J = J0 + j;
+                const uint64_t dk = dk0 + (uint64_t)(((J % NS) * G::kStageBytes) >> 4);
+                const uint32_t d = tmem + (J % NSB) * BN;
 #pragma unroll
                 for (int blk = 0; blk < 4; ++blk) {
 #pragma unroll
@@ -513,30 +537,31 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
                         tc::mma_f16_ss(d, dqr0 + (uint64_t)((k * 32) >> 4),
                                        dk + (uint64_t)((4 * G::kTileBlockBytes + k * 32) >> 4), idesc_s, 1u);
                 }
-                tc::mma_commit(bar_s0 + (j % NSB) * 8);
+                tc::mma_commit(bar_s0 + (J % NSB) * 8);
             };
             // O_r += P C_r(j): A = P(j) from the first 32 columns of score buffer j & 1, B = the first
             // four blocks of the stage as an MN-major operand
             auto issue_pv = [&](int j) {
-                const uint64_t dv = dv0 + (uint64_t)(((j % NS) * G::kStageBytes) >> 4);
-                const uint32_t pa = tmem + (j % NSB) * BN;
+                const int J = J0 + j;
+                const uint64_t dv = dv0 + (uint64_t)(((J % NS) * G::kStageBytes) >> 4);
+                const uint32_t pa = tmem + (J % NSB) * BN;
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k)
                     tc::mma_f16_ts(tmem_o, pa + k * 8, dv + (uint64_t)((k * 2048) >> 4), idesc_o, (j | k) ? 1u : 0u);
-                tc::mma_commit(bar_empty + (j % NS) * 8);
+                tc::mma_commit(bar_empty + (J % NS) * 8);
             };
             auto scores_of = [&](int j) {             // wait for tile j to land, then issue its scores
-                wait_bar(bar_full + (j % NS) * 8, (j / NS) & 1);
+                wait_bar(bar_full + ((J0 + j) % NS) * 8, ((J0 + j) / NS) & 1);
                 tc::fence_async_smem();
                 tc::tc_fence_after();
                 issue_qk(j);
             };
-            wait_bar(bar_q, 0);                      // Q_r is in tensor memory
+            wait_bar(bar_q, item_no & 1);            // this item's Q_r is in tensor memory
             tc::tc_fence_after();
-            scores_of(0);                            // (the rotated block of Q_r rides on full[0])
+            scores_of(0);                            // (the rotated block of Q_r rides on the first tile's barrier)
             if (n_tiles > 1) scores_of(1);
             for (int j = 0; j < n_tiles; ++j) {
-                wait_bar(bar_p, j & 1);              // P(j) is in tensor memory, O rescaled
+                wait_bar(bar_p, (J0 + j) & 1);       // P(j) is in tensor memory, O rescaled
                 tc::tc_fence_after();
                 issue_pv(j);
                 // S(j+2) reuses the buffer of S(j) / P(j): P.C(j) is queued ahead of it and the tensor
@@ -557,6 +582,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         const bool warp_live = quad < live_quads;
 
         if (warp_live) {
+        MLA_STAMP(2 + item_no * 6);
         // ---- latent part of Q_r: global -> registers -> tensor memory.  This thread writes half of
         //      its row (16 columns = 32 elements per step); rows past the last query row are zero ----
         {
@@ -582,10 +608,11 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(bar_q);
         }
+        MLA_STAMP(3 + item_no * 6);
 
         // this thread's 32 columns of the partial scores of tile t: TMEM -> registers -> landing
         // buffer t & 1 of the peer (once the peer has consumed tile t - 2 from it)
-        auto send_partial = [&](int t) {
+        auto send_partial = [&](int t) {             // t: running tile number
             wait_bar(bar_s0 + (t % NSB) * 8, (t / NSB) & 1);
             tc::tc_fence_after();
             uint32_t r[32];
@@ -601,10 +628,11 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         };
         // full scores of 32 columns starting at column c0 of tile j: partial (TMEM) + the peer's
         auto full_scores = [&](int j, int c0, float (&s)[32]) {
+            const int J = J0 + j;
             uint32_t r[32];
-            tc::tmem_ld32(tmem + (j % NSB) * BN + lane_sel + c0, r);
+            tc::tmem_ld32(tmem + (J % NSB) * BN + lane_sel + c0, r);
             tc::tmem_ld_wait();
-            const uint32_t xb = sx + (j & 1) * G::kXBytes + ((c0 / 4) * BM + row_l) * 16;
+            const uint32_t xb = sx + (J & 1) * G::kXBytes + ((c0 / 4) * BM + row_l) * 16;
 #pragma unroll
             for (int c4 = 0; c4 < 8; ++c4) {
                 uint32_t x0, x1, x2, x3;
@@ -634,14 +662,15 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             return fmaxf(tc::max3(a0, a1, a2), a3);
         };
 
-        send_partial(0);
+        send_partial(J0);
         for (int j = 0; j < n_tiles; ++j) {
+            const int J = J0 + j;
             // ---- full scores = mine + the peer's; the other half of the row only for the maximum ----
-            wait_bar(bar_x + (j & 1) * 8, (j >> 1) & 1);
+            wait_bar(bar_x + (J & 1) * 8, (J >> 1) & 1);
             // announce the bytes of tile j + 2 on the same barrier; they cannot land before every
             // warp here has passed the wait above, because the peer sends them only after all
             // warps have released the buffer below
-            if (tid == 0 && j + 2 < n_tiles) tc::mbar_arrive_expect_tx(bar_x + (j & 1) * 8, x_bytes);
+            if (tid == 0 && J + 2 < pair_tiles) tc::mbar_arrive_expect_tx(bar_x + (J & 1) * 8, x_bytes);
             // this thread's half of the row; the two threads of a row swap their maxima through
             // shared memory when the two warps of the lane quadrant meet.  After that meeting both
             // have read S(j) and the landing buffer: the buffer goes back to the peer, and P(j) may
@@ -649,10 +678,10 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             float s[32];
             full_scores(j, hf * HC, s);
             float mx = max_of(s);
-            s_max[j & 1][hf][row_l] = mx;
+            s_max[J & 1][hf][row_l] = mx;
             asm volatile("bar.sync %0, 64;" ::"r"(2 + quad) : "memory");
-            mx = fmaxf(mx, s_max[j & 1][hf ^ 1][row_l]) * p.scale_log2;
-            if (lane == 0) tc::mbar_arrive_remote_relaxed(peer_bar_free + (j & 1) * 8);
+            mx = fmaxf(mx, s_max[J & 1][hf ^ 1][row_l]) * p.scale_log2;
+            if (lane == 0) tc::mbar_arrive_remote_relaxed(peer_bar_free + (J & 1) * 8);
             const bool need = mx > m_run + kRescaleSlack;
             float alpha = 1.f;
             if (need) {
@@ -677,7 +706,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             }
             // ---- O may be rescaled once P.C(j-1) is done ----
             if (j > 0 && __any_sync(0xffffffffu, need)) {   // warp-uniform: TMEM ld/st are collective
-                wait_bar(bar_empty + ((j - 1) % NS) * 8, ((j - 1) / NS) & 1);
+                wait_bar(bar_empty + ((J - 1) % NS) * 8, ((J - 1) / NS) & 1);
                 tc::tc_fence_after();
 #pragma unroll
                 for (int c0 = hf * 128; c0 < (hf + 1) * 128; c0 += 32) {
@@ -690,31 +719,30 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
                 }
             }
             // ---- P(j) goes over the first 32 columns of S(j) ----
-            tc::tmem_st16(tmem + (j % NSB) * BN + lane_sel + hf * (HC / 2), pw);
+            tc::tmem_st16(tmem + (J % NSB) * BN + lane_sel + hf * (HC / 2), pw);
             tc::tmem_st_wait();
             tc::tc_fence_before();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(bar_p);
             // ---- the next tile's partial scores travel while the tensor cores take P(j) ----
-            if (j + 1 < n_tiles) send_partial(j + 1);
+            if (j + 1 < n_tiles) send_partial(J + 1);
+            if (j == 0) MLA_STAMP(4 + item_no * 6);
         }
-        wait_bar(bar_empty + ((n_tiles - 1) % NS) * 8, ((n_tiles - 1) / NS) & 1);
+        MLA_STAMP(5 + item_no * 6);
+        wait_bar(bar_empty + ((J0 + n_tiles - 1) % NS) * 8, ((J0 + n_tiles - 1) / NS) & 1);
         tc::tc_fence_after();
-        }   // live warps
+        MLA_STAMP(6 + item_no * 6);
 
-        // ---- row sum = the two halves (exchanged through an idle landing buffer); store ----
-        // Landing buffer 0 is idle only for warps that consumed every tile of the item: a warp
-        // whose rows are all padding skipped the tile loop and may get here while the peer CTA
-        // still sends tile 0 into that buffer, so it must not write there (its value is never read).
-        float* s_half = reinterpret_cast<float*>(smem + G::kOffX);      // [2][128]
-        if (warp_live) s_half[hf * BM + row_l] = l_run;
-        asm volatile("bar.sync 1, %0;" ::"n"(kMlaTcSoftmaxThreads) : "memory");   // softmax warps only
-        const float l_tot = l_run + s_half[(hf ^ 1) * BM + row_l];
+        // ---- row sum = the two halves, exchanged through shared memory by the live softmax warps
+        //      (the landing buffers are not idle here: the peer may already send the next item's
+        //      first tile); store ----
+        s_half[hf][row_l] = l_run;
+        asm volatile("bar.sync 1, %0;" ::"r"(live_warps * 32) : "memory");
+        const float l_tot = l_run + s_half[hf ^ 1][row_l];
         const float inv = final_out ? (l_tot > 0.f ? 1.f / l_tot : 0.f) : 1.f;
         float* pacc = p.part_acc + ((long long)slot * BM + row_l) * kMlaTcDc + col0;
 #pragma unroll
         for (int c0 = hf * 128; c0 < (hf + 1) * 128; c0 += 32) {
-            if (!warp_live) break;
             uint32_t o[32];
             tc::tmem_ld32(tmem_o + lane_sel + c0, o);
             tc::tmem_ld_wait();
@@ -742,18 +770,22 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             p.part_ml[((long long)slot * BM + row_l) * 2] = m_run;
             p.part_ml[((long long)slot * BM + row_l) * 2 + 1] = l_tot;
         }
+        MLA_STAMP(7 + item_no * 6);
+        }   // live warps
     }
-    // ---- end of the item: nobody re-initialises a barrier, reuses a buffer or leaves while
-    //      the peer may still signal this CTA or write into it ----
+    J0 += n_tiles;
+    ++item_no;
+    }   // items of a range
+    }   // ranges of this pair
+    // ---- nobody leaves while the peer may still signal this CTA or write into it ----
+    MLA_STAMP(62);
+    if (is_loader) cp_async_wait<0>();
     tc::tc_fence_before();
     __syncthreads();
     tc::cluster_sync_all();
     tc::tc_fence_after();
-    }   // items of a range
-    }   // ranges of this pair
-    tc::tc_fence_before();
-    __syncthreads();
     if (warp == 0) tc::tmem_dealloc(tmem, kMlaTcTmemCols);
+    MLA_STAMP(63);
 }
 
 }  // namespace gqa_b200

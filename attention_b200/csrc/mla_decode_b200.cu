@@ -395,6 +395,12 @@ int mla_b200_attend_ex(const void* q_absorbed, const void* q_rope, const void* c
         p.tc_units = (int)units;
         p.tc_row_tiles = (int)(((long long)tq * heads + kMlaTcRows - 1) / kMlaTcRows);
         p.tc_force_range = tc_force_range(capacity, splits);
+        {   // softmax warps whose rows are padding in EVERY unit stay out of the kernel's protocol;
+            // when units differ in their row count (rows per sequence above 128 and not a multiple
+            // of it) all four row groups take part
+            const long long rows_per_seq = (long long)tq * heads;
+            p.tc_live_quads = rows_per_seq <= kMlaTcRows ? (int)((rows_per_seq + 31) / 32) : 4;
+        }
         const TcScratch t = tc_scratch(units, capacity, sms / 2 > 0 ? sms / 2 : 1, p.tc_force_range);
         if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < t.total())
             return GQA_B200_ERR_WORKSPACE;
@@ -487,5 +493,12 @@ int mla_b200_tc_status(int reset) {
     }
     return host;
 }
+
+#ifdef MLA_TC_STAMPS
+// temporary instrumentation: copy the cycle stamps of the last tensor-core attention launch
+GQA_B200_API int mla_b200_debug_stamps(unsigned long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_mla_stamps, sizeof(unsigned long long) * 160 * 64);
+}
+#endif
 
 }  // extern "C"

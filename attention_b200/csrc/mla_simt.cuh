@@ -25,6 +25,7 @@ struct MlaParams {
     int tc_units;              // units = batch * tc_row_tiles; a unit = 128 query rows of one sequence
     int tc_row_tiles;          // ceil(tq * heads / 128)
     int tc_force_range;        // > 0: tiles per range (else total / pairs)
+    int tc_live_quads;         // 32-row groups of a unit that hold query rows in every unit (1..4)
     int page_shift;            // log2(page) when page is a power of two, else -1
     float scale_log2;          // scale * log2(e)
 };

@@ -77,6 +77,9 @@ def parse_args():
     p.add_argument("--seed", type=int, default=42)
     p.add_argument("--kernel", default="auto", choices=["auto", "simt", "mma"])
     p.add_argument("--chunk-tokens", type=int, default=0)
+    p.add_argument("--phases", type=int, default=0,
+                   help="0 = the default path; 7 = plan + decode + merge; 8 = one launch (decode kernel "
+                        "plans and merges); 16 = two launches (self-planning decode, merge)")
     p.add_argument("--cpu-seconds", type=float, default=10.0,
                    help="target CPU time of the cpu_baseline sample")
     p.add_argument("--spinup-seconds", type=float, default=1.0,
@@ -409,7 +412,7 @@ def time_decode(attn, D, sampler, w, inputs, kw, K, W, spin_s):
         marks[0].record()
         for r in range(R):
             for _ in range(K):
-                call()
+                out = call()
             marks[r + 1].record()
         sampler.sample()            # at least one sample while the queue is still draining
         torch.cuda.synchronize()
@@ -418,18 +421,35 @@ def time_decode(attn, D, sampler, w, inputs, kw, K, W, spin_s):
     blocks = [marks[r].elapsed_time(marks[r + 1]) for r in range(R)]
     block_ms = statistics.median(blocks)
 
-    # ---- the decode kernel alone: one call is ONE launch (the kernel plans for itself and the
-    #      last chunk of a sequence merges), so events around single calls on the launching
-    #      stream give the kernel's launch duration ----
+    # ---- the decode kernel alone, its own events on the launching stream: the self-planning
+    #      decode kernel is launched by itself (phases 32) between the two events and the merge
+    #      kernel (phases 4) after the closing one; above 2048 sequences plan / decode / merge ----
+    ws = torch.zeros(attn.workspace_bytes(w.batch, w.q_heads, w.kv_heads, w.head_dim, w.block_size,
+                                          table.shape[1], kw.get("chunk_tokens", 0)),
+                     dtype=torch.uint8, device=q.device)
+    out2 = torch.empty_like(q)
+    kwk = {k_: v_ for k_, v_ in kw.items() if k_ != "phases"}
+    self_plan = w.batch <= 2048
     n_k = max(K, min(200, int(math.ceil(20.0 / max(1e-3, est_ms)))))
     pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
              for _ in range(n_k)]
     for a, b in pairs:
-        a.record()
-        call()
-        b.record()
+        kk, vv = pools[calls[0] % n_pools]
+        calls[0] += 1
+        if self_plan:
+            a.record()
+            attn.gqa_decode(q, kk, vv, table, lens, out=out2, workspace=ws, phases=32, **kwk)
+            b.record()
+        else:
+            attn.gqa_decode(q, kk, vv, table, lens, out=out2, workspace=ws, phases=1, **kwk)
+            a.record()
+            attn.gqa_decode(q, kk, vv, table, lens, out=out2, workspace=ws, phases=2, **kwk)
+            b.record()
+        attn.gqa_decode(q, kk, vv, table, lens, out=out2, workspace=ws, phases=4, **kwk)
     torch.cuda.synchronize()
     kernel_ms = statistics.median(a.elapsed_time(b) for a, b in pairs)
+    if kw.get("phases", 0) in (0, 16):
+        assert torch.equal(out, out2), "phased launches must reproduce the one-call result"
 
     # ---- e2e: a decode step through the public API with per-step inputs in pinned host
     #      memory: H2D of q, the new token's key/value, block table, lengths; kv_append;
@@ -583,7 +603,7 @@ def run_b200(args):
     D.init()
     peak, peak_src = measured_peak()
     sampler = ClockSampler(physical_gpu_index(D.local_rank))
-    kw = dict(kernel=args.kernel, chunk_tokens=args.chunk_tokens)
+    kw = dict(kernel=args.kernel, chunk_tokens=args.chunk_tokens, phases=args.phases)
     K, W = args.steps, max(args.warmup, 3)
     extras = not args.only_headline
 
@@ -632,7 +652,8 @@ def run_b200(args):
         D.close()
         return
 
-    launches_per_step = 1 if w.batch <= 2048 else 3     # one launch per call up to 2048 sequences
+    # decode + merge kernels per call (one launch for small static shapes, three above 2048 sequences)
+    launches_per_step = {7: 3, 8: 1, 16: 2}.get(args.phases, 2 if w.batch <= 2048 else 3)
     line = {
         "metric": METRIC, "value": head["value"], "unit": UNIT, "n_gpus": D.world, "steps": K,
         "warmup": W, "ms_per_step": head["ms_per_step"], "us_per_call": head["us_per_call"],

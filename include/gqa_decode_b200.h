@@ -127,14 +127,17 @@ GQA_B200_API int gqa_b200_workspace_init(void* workspace, size_t workspace_bytes
  * Replaces gqa_decode_cuda (csrc/binding/torch_ops.cpp:5-11,
  * csrc/cuda/dense/gqa_decode.cu:186-188) and, through it, gqa_decode_impl
  * (gqa_decode.cu:96-183) with its two kernels (gqa_decode.cu:18-87).
- * ONE launch on `stream` for batches of up to 2048 sequences (and at most
- * 16384 (sequence, kv head) pairs): every persistent
- * decode CTA cuts the sequences into KV chunks itself from context_lens (never
- * read by the host), pulls (sequence, chunk, kv head) items from a counter --
- * every K/V row is read once for all query heads of its group -- and the CTA
- * that finishes the last chunk of a sequence folds that sequence's partials
- * (log-sum-exp, in slot order) into `out`.  Larger batches take three launches:
- * plan, decode, merge.  Empty sequences get zero rows.
+ * No plan launch for batches of up to 2048 sequences: every persistent decode
+ * CTA cuts the sequences into KV chunks itself from context_lens (never read by
+ * the host) and pulls (sequence, chunk, kv head) items from a counter -- every
+ * K/V row is read once for all query heads of its group.  Sequences of several
+ * chunks leave fp32 partials; the merge kernel (a second launch) folds them,
+ * log-sum-exp, in slot order.  When the static shape is small enough for every
+ * work item to get a CTA of its own (small batches of short tables), there is
+ * ONE launch: the CTA that takes the last ticket of a sequence merges it.
+ * Batches above 2048 sequences take three launches: plan, decode, merge.  All
+ * three paths cut a sequence the same way and give the same bits for the same
+ * chunk_tokens.  Empty sequences get zero rows.
  * batch == 0 returns OK without launching (gqa_decode.cu:142). */
 GQA_B200_API int gqa_b200_decode(const void* q, const void* k_cache, const void* v_cache,
                                  const int32_t* block_table, const int32_t* context_lens,
@@ -143,22 +146,26 @@ GQA_B200_API int gqa_b200_decode(const void* q, const void* k_cache, const void*
                                  float scale, void* workspace, size_t workspace_bytes,
                                  void* stream);
 
-/* phases of gqa_b200_decode_ex: 0 = the default path (one launch when the batch
- * allows it); a bit mask selects launches of the three-launch path, 7 = all three */
+/* phases of gqa_b200_decode_ex: 0 = the default path, chosen from the static
+ * shape (see gqa_b200_decode); bits 1, 2, 4 select launches of the three-launch
+ * path (7 = all three); 8 or 16 alone force the one- or the two-launch path; 32 then
+ * 4 are the two launches of the two-launch path, one per call */
 #define GQA_B200_PHASE_PLAN 1
 #define GQA_B200_PHASE_DECODE 2
 #define GQA_B200_PHASE_MERGE 4
+#define GQA_B200_PHASE_ONE_LAUNCH 8  /* alone: self-planning decode kernel that also merges   */
+#define GQA_B200_PHASE_TWO_LAUNCH 16 /* alone: self-planning decode kernel, then merge kernel */
+#define GQA_B200_PHASE_SELF_DECODE 32 /* alone: the self-planning decode kernel only; a call
+                                         with GQA_B200_PHASE_MERGE must follow (timing aid) */
 
 /* Same operator with explicit tuning knobs (tests, benchmarks):
  *   chunk_tokens  base KV-chunk length (0 = built-in; otherwise 16..65536)
  *   kernel        GQA_B200_KERNEL_*
  *   max_ctas      cap on the persistent grid (0 = SM count x resident CTAs)
- *   phases        0 = default; otherwise which launches of the three-launch
- *                 path to enqueue (GQA_B200_PHASE_*).  A benchmark uses it to put
- *                 its own events around the decode kernel; the phases of one call
- *                 must still run in order plan, decode, merge on the same
- *                 workspace.  The three-launch path gives the same bits as the
- *                 one-launch path for the same chunk_tokens.                    */
+ *   phases        0 = default; GQA_B200_PHASE_* otherwise.  A benchmark uses the
+ *                 bits 1, 2, 4 to put its own events around the decode kernel;
+ *                 the phases of one call must still run in order plan, decode,
+ *                 merge on the same workspace.                                 */
 GQA_B200_API int gqa_b200_decode_ex(const void* q, const void* k_cache, const void* v_cache,
                                     const int32_t* block_table, const int32_t* context_lens,
                                     void* out, int dtype, int batch, int q_heads, int kv_heads,

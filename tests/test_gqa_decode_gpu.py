@@ -163,10 +163,11 @@ def test_out_and_workspace_arguments():
     hdr = ws[:20].view(torch.int32).cpu()
     assert int(hdr[2]) == 0 and int(hdr[1]) == sum(-(-n // 64) for n in (300, 40, 1000))
     assert int(hdr[0]) == 0 and int(hdr[4]) == 0               # counters back at zero
-    # the three-launch path on the same workspace, and the one-launch path after it
+    # the three-launch path on the same workspace, and the one- and two-launch paths after it
     out3 = attn.gqa_decode(*args, workspace=ws, chunk_tokens=64, phases=7)
     assert torch.equal(out3, out)
-    assert torch.equal(attn.gqa_decode(*args, workspace=ws, chunk_tokens=64), out)
+    assert torch.equal(attn.gqa_decode(*args, workspace=ws, chunk_tokens=64, phases=8), out)
+    assert torch.equal(attn.gqa_decode(*args, workspace=ws, chunk_tokens=64, phases=16), out)
     small = torch.empty(need - 256, dtype=torch.uint8, device=DEV)
     with pytest.raises(RuntimeError, match="workspace"):
         attn.gqa_decode(*args, workspace=small, chunk_tokens=64)
@@ -345,24 +346,44 @@ def test_randomized_shapes_against_oracle():
                       f"chunk={chunk} {kernel}")
 
 
-# --------------------------------------------------------------------------- one launch vs three
+# --------------------------------------------------------------------------- one, two, three launches
+ONE_LAUNCH, TWO_LAUNCH, THREE_LAUNCH = 8, 16, 7     # `phases` values that force a path
+
+
 @pytest.mark.parametrize("kernel", ["auto", "simt"])
 @pytest.mark.parametrize("chunk", [0, 16, 64, 512])
-def test_one_launch_and_three_launch_paths_agree(kernel, chunk):
+def test_one_two_and_three_launch_paths_agree(kernel, chunk):
     """Same chunk list, same partial slots, same merge arithmetic: with an explicit chunk length
-    the two paths give identical bits; with the automatic one (the two paths may pick different
-    bases) they agree within the tolerance."""
+    the three paths give identical bits; with the automatic one (the plan kernel and the
+    self-planning decode kernel may pick different bases) they agree within the tolerance."""
     lengths = [0, 1, 15, 16, 17, 300, 0, 1000, 64, 2500, 33, 4097, 5]
     for dtype, hq, hkv in ((torch.bfloat16, 32, 8), (torch.float16, 28, 4), (torch.float32, 8, 2)):
         q, k, v, table, lens = _make_case(lengths, hq, hkv, 128, 16, dtype, seed=chunk + hq)
         args = _cuda(q, k, v, table, lens)
-        one = attn.gqa_decode(*args, kernel=kernel, chunk_tokens=chunk)
-        three = attn.gqa_decode(*args, kernel=kernel, chunk_tokens=chunk, phases=7)
+        one = attn.gqa_decode(*args, kernel=kernel, chunk_tokens=chunk, phases=ONE_LAUNCH)
+        two = attn.gqa_decode(*args, kernel=kernel, chunk_tokens=chunk, phases=TWO_LAUNCH)
+        three = attn.gqa_decode(*args, kernel=kernel, chunk_tokens=chunk, phases=THREE_LAUNCH)
+        default = attn.gqa_decode(*args, kernel=kernel, chunk_tokens=chunk)
+        assert torch.equal(one, two), f"{dtype} {kernel} chunk={chunk}"
+        assert torch.equal(default, two), f"{dtype} {kernel} chunk={chunk}"
         if chunk:
             assert torch.equal(one, three), f"{dtype} {kernel} chunk={chunk}"
         _assert_close(one, three, dtype)
         _assert_close(one, _oracle(*args), dtype, f"{dtype} {kernel} chunk={chunk}")
         assert torch.count_nonzero(one[0]) == 0 and torch.count_nonzero(one[6]) == 0
+
+
+def test_default_path_follows_the_static_shape():
+    """A batch whose every possible work item fits a CTA of its own takes one launch (the
+    workspace's plan words are written, no merge launch is needed); a larger table takes two."""
+    q, k, v, table, lens = _make_case([300, 40, 500], 8, 2, 128, 16, torch.bfloat16, seed=8)
+    args = _cuda(q, k, v, table, lens)
+    want = _oracle(*args)
+    _assert_close(attn.gqa_decode(*args), want, torch.bfloat16, "small table")
+    wide = torch.full((3, 4096), -1, dtype=torch.int32)
+    wide[:, : table.shape[1]] = table
+    args_wide = _cuda(q, k, v, wide, lens)
+    _assert_close(attn.gqa_decode(*args_wide), want, torch.bfloat16, "wide table")
 
 
 def test_one_launch_path_leaves_the_workspace_clean():
@@ -380,7 +401,7 @@ def test_one_launch_path_leaves_the_workspace_clean():
         for chunk in (0, 64):
             if attn.workspace_bytes(6, 32, 8, 128, 16, 400, chunk) > lib_need:
                 continue
-            got = attn.gqa_decode(*args, workspace=ws, chunk_tokens=chunk)
+            got = attn.gqa_decode(*args, workspace=ws, chunk_tokens=chunk, phases=ONE_LAUNCH)
             _assert_close(got, _oracle(*args), torch.bfloat16, f"{lengths} chunk={chunk}")
             words = ws[:control].view(torch.int32).cpu()
             assert int(words[0]) == 0 and int(words[4]) == 0, "counters not released"
@@ -400,11 +421,12 @@ def test_calls_of_different_shapes_share_one_workspace():
         q, k, v, table, lens = _make_case(lengths, hq, hkv, d, 16, dtype, seed=i)
         args = _cuda(q, k, v, table, lens)
         for kernel in ("auto", "simt"):
-            got = attn.gqa_decode(*args, workspace=ws, kernel=kernel)
-            _assert_close(got, _oracle(*args), dtype, f"shape {i} {kernel}")
+            for phases in (0, ONE_LAUNCH, TWO_LAUNCH, THREE_LAUNCH):
+                got = attn.gqa_decode(*args, workspace=ws, kernel=kernel, phases=phases)
+                _assert_close(got, _oracle(*args), dtype, f"shape {i} {kernel} phases={phases}")
 
 
-def test_batches_beyond_the_one_launch_limit_take_three_launches():
+def test_batches_beyond_the_self_planning_limit_take_three_launches():
     """More than 2048 sequences: the prefix array no longer fits the decode CTA's shared memory,
     the call falls back to plan + decode + merge."""
     gen = torch.Generator().manual_seed(11)
