@@ -118,6 +118,9 @@ template <int D, int TILE_N, int NSTAGES, int NWARPS> struct MmaGeom {
     static constexpr int kFixedBytes = NWARPS * kWarpBytes + kQBytes + 2 * NWARPS * 16 * 4;
     static_assert(kChunksPerRow <= 32 && 32 % kChunksPerRow == 0, "row must fit a warp pass");
     static_assert(16 * kOStride * 4 <= kWarpBytes, "combine scratch must fit the warp's ring");
+    // the tile fetched ahead for the next item lives in the last stage while the combine of
+    // the current item uses the first bytes of the ring
+    static_assert(16 * kOStride * 4 <= (NSTAGES - 1) * kStageBytes, "combine scratch overlaps the prefetch stage");
     static_assert(TILE_N % 16 == 0, "tile is a multiple of the mma K step");
 };
 
@@ -128,6 +131,18 @@ template <int D, int TILE_N, int NSTAGES, int NWARPS> struct MmaGeom {
 // fp32 and well inside fp16/bf16 range; (m, l, O) stay mutually consistent, so
 // the normalised result is unchanged.
 constexpr float kRescaleSlack = 8.f;
+
+#ifdef GQA_STAMPS
+__device__ unsigned long long g_gqa_stamps[320 * 64];
+__device__ __forceinline__ unsigned long long gqa_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define GQA_STAMP(k) do { if (threadIdx.x == 0 && (k) < 64 && blockIdx.x < 320) g_gqa_stamps[blockIdx.x * 64 + (k)] = gqa_now(); } while (0)
+#else
+#define GQA_STAMP(k) do {} while (0)
+#endif
 
 template <typename T, int D, int TILE_N, int NSTAGES, int NWARPS, int MIN_CTAS, int CP_MODE = 3>
 __global__ void __launch_bounds__(NWARPS * 32, MIN_CTAS)
@@ -154,6 +169,7 @@ gqa_decode_mma_kernel(const DecodeParams p) {
     int* s_table = reinterpret_cast<int*>(s_l + NWARPS * 16);           // [table_smem_entries]
     int* s_off = s_table + p.table_smem_entries;                         // fused mode: [batch + 1]
     __shared__ int s_item;
+    __shared__ unsigned long long s_ahead;   // (sequence number of the current item << 32) | next item
     __shared__ FusedPending s_pending;
     __shared__ int s_red[2 * kNumAutoBases * 32 + 32];
 
@@ -170,6 +186,8 @@ gqa_decode_mma_kernel(const DecodeParams p) {
     const uint64_t policy = CP_MODE >= 3 ? evict_first_policy() : 0;
     pdl_launch_dependents();
     pdl_wait();   // the plan kernel wrote hdr / items; the call before left the counters at zero
+    GQA_STAMP(0);
+    int stamp_item = 0;
     const bool fused = p.mode == kModeFused;
     const bool tickets = fused && p.fused_merge;   // merge inside this kernel
     const bool counted = p.mode != kModeRefSplits;      // items are pulled from the work counter
@@ -203,9 +221,19 @@ gqa_decode_mma_kernel(const DecodeParams p) {
     } else {
         item = blockIdx.x;
     }
+    GQA_STAMP(1);
     int4 rec = make_int4(0, 0, 0, 0);
     if (!fused && item < n_items) rec = load_item_record(p, item);
     int n_pend = 0;     // one-launch mode: multi-chunk items whose tickets are still to be taken
+    // Cross-item prefetch (self-planning mode): when a warp has finished its tiles of an item it
+    // already requests its first tile of the CTA's NEXT item, into the ring stage the combine does
+    // not use, so the data travels during the combine, the partial store and the next item's
+    // set-up (measured before this: 2 - 3 us from the start of an item to its first tile, 15 -
+    // 30 % of an item of a few hundred tokens).  Tile k of every item lives in stage
+    // (k + NSTAGES - 1) % NSTAGES, so tile 0 is in the last stage.
+    unsigned int seq = 0;          // items this CTA has started
+    int pf_item = -1;              // item whose tile 0 this warp has already requested
+    if (tid == 0) s_ahead = ~0ull;
 
     while (item < n_items) {
         int next = 0;
@@ -217,6 +245,7 @@ gqa_decode_mma_kernel(const DecodeParams p) {
         const WorkItem w = fused ? fused_item(p, item, s_off, plan.base) : item_from_record(p, item, rec);
         const int rows_valid = min(16, p.group - w.hg * 16);
         const bool nonempty = w.t1 > w.t0;
+        GQA_STAMP(2 + stamp_item * 3);
 
         if (nonempty) {
             // ---- Q fragments (A operand: rows = query heads, padded with zeros) ----
@@ -260,14 +289,17 @@ gqa_decode_mma_kernel(const DecodeParams p) {
                 const int n_tiles = (s1 - s0 + TILE_N - 1) / TILE_N;
                 const int my_tiles = n_tiles > warp ? (n_tiles - warp + NWARPS - 1) / NWARPS : 0;
                 const bool fast_segment = pages_hold_subtiles && (s0 & 15) == 0;
+                const bool pf_here = pf_item == item && s0 == w.t0;   // this warp's tile 0 is on its way
 
                 // issue the copies of this warp's k-th tile (and always commit a group)
                 auto issue = [&](int k) {
                     if (k < my_tiles) {
                         const int tile_t0 = s0 + (warp + k * NWARPS) * TILE_N;
-                        const uint32_t sk = ring_u32 + (k % NSTAGES) * G::kStageBytes;
+                        const uint32_t sk = ring_u32 + ((k + NSTAGES - 1) % NSTAGES) * G::kStageBytes;
                         const uint32_t sv = sk + G::kTileBytes;
-                        if (fast_segment && tile_t0 + TILE_N <= s1) {
+                        if (k == 0 && pf_here) {
+                            // requested at the end of the previous item
+                        } else if (fast_segment && tile_t0 + TILE_N <= s1) {
                             // whole tile valid, each 16-token sub-tile inside one page: one
                             // table lookup per sub-tile, then a constant source stride
 #pragma unroll
@@ -333,10 +365,15 @@ gqa_decode_mma_kernel(const DecodeParams p) {
                 for (int k = 0; k < my_tiles; ++k) {
                     cp_async_wait<NSTAGES - 2>();   // this lane's copies of tile k have landed
                     __syncwarp();                   // ... and every lane's; tile k-1 fully consumed
+                    if (k == 0 && s0 == w.t0) GQA_STAMP(3 + stamp_item * 3);
+                    // (by now the work counter has answered: every warp may learn the next item)
+                    if (counted && tid == 0 && k == 0 && s0 == w.t0)
+                        *reinterpret_cast<volatile unsigned long long*>(&s_ahead) =
+                            ((unsigned long long)seq << 32) | (unsigned int)next;
                     issue(k + NSTAGES - 1);         // refill the stage tile k-1 used
 
                     const int tile_t0 = s0 + (warp + k * NWARPS) * TILE_N;
-                    const uint32_t sk = ring_u32 + (k % NSTAGES) * G::kStageBytes;
+                    const uint32_t sk = ring_u32 + ((k + NSTAGES - 1) % NSTAGES) * G::kStageBytes;
                     const uint32_t sv = sk + G::kTileBytes;
 
                     // ---- S = Q K^T : [16 heads] x [TILE_N tokens] ----
@@ -437,6 +474,45 @@ gqa_decode_mma_kernel(const DecodeParams p) {
                 cp_async_wait<0>();
             }
 
+            // ---- this warp's first tile of the CTA's next item (see pf_item above) ----
+            // (not in the one-launch mode: its merges stage partials through the whole ring)
+            if (fused && !tickets && pages_hold_subtiles) {
+                const unsigned long long ahead = *reinterpret_cast<volatile unsigned long long*>(&s_ahead);
+                const int cand = (int)(unsigned int)ahead;
+                if ((unsigned int)(ahead >> 32) == seq && cand < n_items) {
+                    const WorkItem wn = fused_item(p, cand, s_off, plan.base);
+                    const int tile_t0 = wn.t0 + warp * TILE_N;
+                    if ((wn.t0 & 15) == 0 && wn.t1 - wn.t0 <= p.seg_tokens && tile_t0 + TILE_N <= wn.t1) {
+                        const uint32_t sk = ring_u32 + (NSTAGES - 1) * G::kStageBytes;
+                        const uint32_t sv = sk + G::kTileBytes;
+                        const int32_t* trow = p.table + (long long)wn.b * p.max_pages;
+                        const int last_block = (int)(p.num_blocks - 1);
+#pragma unroll
+                        for (int sub = 0; sub < TILE_N / 16; ++sub) {
+                            const int t = tile_t0 + sub * 16;
+                            int pg = __ldg(trow + (t >> p.bs_shift));
+                            pg = pg < 0 ? 0 : (pg > last_block ? last_block : pg);   // as stage_table
+                            const int slot = (t & (p.block_size - 1)) + ld_row;
+                            const long long off = ((long long)pg * p.block_size + slot) * row_bytes_all +
+                                                  (long long)wn.kvh * ROWB + ld_cc * 16;
+                            const char* ks = kc + off;
+                            const char* vs = vc + off;
+#pragma unroll
+                            for (int it = 0; it < SUB_ITERS; ++it) {
+                                const int row = sub * 16 + it * ROWS_PER_IT + ld_row;
+                                const uint32_t dst = row * ROWB + ((ld_cc ^ (row & 7)) << 4);
+                                cp_async16<CP_MODE>(sk + dst, ks, 16, policy);
+                                cp_async16<CP_MODE>(sv + dst, vs, 16, policy);
+                                ks += ROWS_PER_IT * row_bytes_all;
+                                vs += ROWS_PER_IT * row_bytes_all;
+                            }
+                        }
+                        cp_async_commit();
+                        pf_item = cand;
+                    }
+                }
+            }
+
             // ---- publish this warp's state ----
             l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
             l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -458,6 +534,8 @@ gqa_decode_mma_kernel(const DecodeParams p) {
                 s_l[warp * 16 + r0 + 8] = l1;
             }
         }
+        GQA_STAMP(4 + stamp_item * 3);
+        ++stamp_item;
         if (tid == 0) s_item = next;
         __syncthreads();
         // fetch the next item's record now; its latency hides behind the combine
@@ -481,9 +559,12 @@ gqa_decode_mma_kernel(const DecodeParams p) {
         }
         item = nxt;
         rec = rec_next;
+        ++seq;
     }
     if (tickets) fused_flush_tickets<T, true, true>(p, s_pending, n_pend, s_ring, NWARPS * G::kWarpBytes);
+    GQA_STAMP(62);
     if (counted) decode_counters_release(p);
+    GQA_STAMP(63);
 }
 
 }  // namespace gqa_b200

@@ -382,6 +382,50 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     bool alive = true;
     int J0 = 0;                                      // running number of the item's first tile
     int item_no = 0;                                 // items of this pair so far
+    // The rows of an item are not stored when its last tile is done but at the start of the next
+    // item, after that item's queries have gone to tensor memory: the tensor cores then compute the
+    // next item's first scores while the softmax threads move the finished accumulators out.
+    // (Nothing writes O before P.C of the next item's first tile, which waits for every softmax
+    // warp's P, i.e. until after its store.)
+    const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+    bool st_pending = false, st_final = false, st_write = false;
+    int st_slot = 0;
+    long long st_grow = 0;
+    float st_inv = 1.f, st_m = 0.f, st_l = 0.f;
+    auto store_rows = [&]() {
+        float* pacc = p.part_acc + ((long long)st_slot * BM + row_l) * kMlaTcDc + col0;
+#pragma unroll
+        for (int c0 = hf * 128; c0 < (hf + 1) * 128; c0 += 32) {
+            uint32_t o[32];
+            tc::tmem_ld32(tmem_o + lane_sel + c0, o);
+            tc::tmem_ld_wait();
+            if (st_write) {
+                if (st_final) {
+                    uint4* dst = reinterpret_cast<uint4*>(op + st_grow * kMlaTcDc + col0 + c0);
+#pragma unroll
+                    for (int c8 = 0; c8 < 4; ++c8) {
+                        uint4 v;
+                        v.x = Ops::pack(__uint_as_float(o[c8 * 8 + 0]) * st_inv, __uint_as_float(o[c8 * 8 + 1]) * st_inv);
+                        v.y = Ops::pack(__uint_as_float(o[c8 * 8 + 2]) * st_inv, __uint_as_float(o[c8 * 8 + 3]) * st_inv);
+                        v.z = Ops::pack(__uint_as_float(o[c8 * 8 + 4]) * st_inv, __uint_as_float(o[c8 * 8 + 5]) * st_inv);
+                        v.w = Ops::pack(__uint_as_float(o[c8 * 8 + 6]) * st_inv, __uint_as_float(o[c8 * 8 + 7]) * st_inv);
+                        dst[c8] = v;
+                    }
+                } else {
+                    uint4* dst = reinterpret_cast<uint4*>(pacc + c0);
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4)
+                        dst[c4] = make_uint4(o[c4 * 4], o[c4 * 4 + 1], o[c4 * 4 + 2], o[c4 * 4 + 3]);
+                }
+            }
+        }
+        if (!st_final && st_write && rank == 0 && hf == 0) {
+            p.part_ml[((long long)st_slot * BM + row_l) * 2] = st_m;
+            p.part_ml[((long long)st_slot * BM + row_l) * 2 + 1] = st_l;
+        }
+        tc::tc_fence_before();                       // the loads of O are done before the barrier arrivals below
+        st_pending = false;
+    };
     for (int range = blockIdx.x >> 1; range < n_ranges; range += gridDim.x >> 1) {
     int pos = range * per_range;
     const int range_end = min(total_tiles, pos + per_range);
@@ -575,7 +619,6 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         const uint32_t peer_sx = tc::map_to_cta(sx, peer);
         const uint32_t peer_bar_x = tc::map_to_cta(bar_x, peer);
         const uint32_t peer_bar_free = tc::map_to_cta(bar_free, peer);
-        const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
         const int my_end = g < R ? mla_row_end(p, b, g / p.heads) : 0;
         const int my_stop = min(my_end, t1);         // this row sees tokens [t0, my_stop) of the chunk
         float m_run = -INFINITY, l_run = 0.f;
@@ -587,27 +630,31 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         //      its row (16 columns = 32 elements per step); rows past the last query row are zero ----
         {
             const T* qa = reinterpret_cast<const T*>(p.q) + grow * kMlaTcDc + col0 + hf * 128;
+            // two batches of eight 16-byte loads, each batch issued before its first use (one
+            // memory round trip per batch instead of one per step)
 #pragma unroll
-            for (int st = 0; st < 4; ++st) {
-                uint32_t w[16];
-                if (g < R) {
-                    const uint4* src = reinterpret_cast<const uint4*>(qa + st * 32);
+            for (int half = 0; half < 2; ++half) {
+                uint4 v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    v[i] = g < R ? __ldg(reinterpret_cast<const uint4*>(qa + half * 64) + i) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                for (int st = 0; st < 2; ++st) {
+                    uint32_t w[16];
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
-                        const uint4 v = __ldg(src + q4);
-                        w[q4 * 4] = v.x; w[q4 * 4 + 1] = v.y; w[q4 * 4 + 2] = v.z; w[q4 * 4 + 3] = v.w;
+                        w[q4 * 4] = v[st * 4 + q4].x; w[q4 * 4 + 1] = v[st * 4 + q4].y;
+                        w[q4 * 4 + 2] = v[st * 4 + q4].z; w[q4 * 4 + 3] = v[st * 4 + q4].w;
                     }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) w[c] = 0u;
+                    tc::tmem_st16(tmem_q + lane_sel + hf * 64 + (half * 2 + st) * 16, w);
                 }
-                tc::tmem_st16(tmem_q + lane_sel + hf * 64 + st * 16, w);
             }
             tc::tmem_st_wait();
             tc::tc_fence_before();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(bar_q);
         }
+        if (st_pending) store_rows();                // the previous item's rows (see above)
         MLA_STAMP(3 + item_no * 6);
 
         // this thread's 32 columns of the partial scores of tile t: TMEM -> registers -> landing
@@ -739,37 +786,14 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         s_half[hf][row_l] = l_run;
         asm volatile("bar.sync 1, %0;" ::"r"(live_warps * 32) : "memory");
         const float l_tot = l_run + s_half[hf ^ 1][row_l];
-        const float inv = final_out ? (l_tot > 0.f ? 1.f / l_tot : 0.f) : 1.f;
-        float* pacc = p.part_acc + ((long long)slot * BM + row_l) * kMlaTcDc + col0;
-#pragma unroll
-        for (int c0 = hf * 128; c0 < (hf + 1) * 128; c0 += 32) {
-            uint32_t o[32];
-            tc::tmem_ld32(tmem_o + lane_sel + c0, o);
-            tc::tmem_ld_wait();
-            if (g < R && alive) {
-                if (final_out) {
-                    uint4* dst = reinterpret_cast<uint4*>(op + grow * kMlaTcDc + col0 + c0);
-#pragma unroll
-                    for (int c8 = 0; c8 < 4; ++c8) {
-                        uint4 v;
-                        v.x = Ops::pack(__uint_as_float(o[c8 * 8 + 0]) * inv, __uint_as_float(o[c8 * 8 + 1]) * inv);
-                        v.y = Ops::pack(__uint_as_float(o[c8 * 8 + 2]) * inv, __uint_as_float(o[c8 * 8 + 3]) * inv);
-                        v.z = Ops::pack(__uint_as_float(o[c8 * 8 + 4]) * inv, __uint_as_float(o[c8 * 8 + 5]) * inv);
-                        v.w = Ops::pack(__uint_as_float(o[c8 * 8 + 6]) * inv, __uint_as_float(o[c8 * 8 + 7]) * inv);
-                        dst[c8] = v;
-                    }
-                } else {
-                    uint4* dst = reinterpret_cast<uint4*>(pacc + c0);
-#pragma unroll
-                    for (int c4 = 0; c4 < 8; ++c4)
-                        dst[c4] = make_uint4(o[c4 * 4], o[c4 * 4 + 1], o[c4 * 4 + 2], o[c4 * 4 + 3]);
-                }
-            }
-        }
-        if (!final_out && g < R && alive && rank == 0 && hf == 0) {
-            p.part_ml[((long long)slot * BM + row_l) * 2] = m_run;
-            p.part_ml[((long long)slot * BM + row_l) * 2 + 1] = l_tot;
-        }
+        st_final = final_out;
+        st_inv = final_out ? (l_tot > 0.f ? 1.f / l_tot : 0.f) : 1.f;
+        st_slot = slot;
+        st_grow = grow;
+        st_write = g < R && alive;
+        st_m = m_run;
+        st_l = l_tot;
+        st_pending = true;
         MLA_STAMP(7 + item_no * 6);
         }   // live warps
     }
@@ -777,6 +801,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     ++item_no;
     }   // items of a range
     }   // ranges of this pair
+    if (st_pending) store_rows();                    // the last item's rows
     // ---- nobody leaves while the peer may still signal this CTA or write into it ----
     MLA_STAMP(62);
     if (is_loader) cp_async_wait<0>();
