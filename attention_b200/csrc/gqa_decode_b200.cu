@@ -427,13 +427,6 @@ extern "C" {
 
 int gqa_b200_abi_version(void) { return GQA_B200_ABI_VERSION; }
 
-#ifdef GQA_STAMPS
-// temporary instrumentation: copy the time stamps of the last tensor-core decode launch
-GQA_B200_API int gqa_b200_debug_stamps(unsigned long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_gqa_stamps, sizeof(unsigned long long) * 320 * 64);
-}
-#endif
-
 const char* gqa_b200_strerror(int code) {
     switch (code) {
         case GQA_B200_OK: return "ok";

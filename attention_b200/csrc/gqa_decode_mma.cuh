@@ -132,18 +132,6 @@ template <int D, int TILE_N, int NSTAGES, int NWARPS> struct MmaGeom {
 // the normalised result is unchanged.
 constexpr float kRescaleSlack = 8.f;
 
-#ifdef GQA_STAMPS
-__device__ unsigned long long g_gqa_stamps[320 * 64];
-__device__ __forceinline__ unsigned long long gqa_now() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define GQA_STAMP(k) do { if (threadIdx.x == 0 && (k) < 64 && blockIdx.x < 320) g_gqa_stamps[blockIdx.x * 64 + (k)] = gqa_now(); } while (0)
-#else
-#define GQA_STAMP(k) do {} while (0)
-#endif
-
 template <typename T, int D, int TILE_N, int NSTAGES, int NWARPS, int MIN_CTAS, int CP_MODE = 3>
 __global__ void __launch_bounds__(NWARPS * 32, MIN_CTAS)
 gqa_decode_mma_kernel(const DecodeParams p) {
@@ -186,8 +174,6 @@ gqa_decode_mma_kernel(const DecodeParams p) {
     const uint64_t policy = CP_MODE >= 3 ? evict_first_policy() : 0;
     pdl_launch_dependents();
     pdl_wait();   // the plan kernel wrote hdr / items; the call before left the counters at zero
-    GQA_STAMP(0);
-    int stamp_item = 0;
     const bool fused = p.mode == kModeFused;
     const bool tickets = fused && p.fused_merge;   // merge inside this kernel
     const bool counted = p.mode != kModeRefSplits;      // items are pulled from the work counter
@@ -221,7 +207,6 @@ gqa_decode_mma_kernel(const DecodeParams p) {
     } else {
         item = blockIdx.x;
     }
-    GQA_STAMP(1);
     int4 rec = make_int4(0, 0, 0, 0);
     if (!fused && item < n_items) rec = load_item_record(p, item);
     int n_pend = 0;     // one-launch mode: multi-chunk items whose tickets are still to be taken
@@ -245,7 +230,6 @@ gqa_decode_mma_kernel(const DecodeParams p) {
         const WorkItem w = fused ? fused_item(p, item, s_off, plan.base) : item_from_record(p, item, rec);
         const int rows_valid = min(16, p.group - w.hg * 16);
         const bool nonempty = w.t1 > w.t0;
-        GQA_STAMP(2 + stamp_item * 3);
 
         if (nonempty) {
             // ---- Q fragments (A operand: rows = query heads, padded with zeros) ----
@@ -365,7 +349,6 @@ gqa_decode_mma_kernel(const DecodeParams p) {
                 for (int k = 0; k < my_tiles; ++k) {
                     cp_async_wait<NSTAGES - 2>();   // this lane's copies of tile k have landed
                     __syncwarp();                   // ... and every lane's; tile k-1 fully consumed
-                    if (k == 0 && s0 == w.t0) GQA_STAMP(3 + stamp_item * 3);
                     // (by now the work counter has answered: every warp may learn the next item)
                     if (counted && tid == 0 && k == 0 && s0 == w.t0)
                         *reinterpret_cast<volatile unsigned long long*>(&s_ahead) =
@@ -534,8 +517,6 @@ gqa_decode_mma_kernel(const DecodeParams p) {
                 s_l[warp * 16 + r0 + 8] = l1;
             }
         }
-        GQA_STAMP(4 + stamp_item * 3);
-        ++stamp_item;
         if (tid == 0) s_item = next;
         __syncthreads();
         // fetch the next item's record now; its latency hides behind the combine
@@ -562,9 +543,7 @@ gqa_decode_mma_kernel(const DecodeParams p) {
         ++seq;
     }
     if (tickets) fused_flush_tickets<T, true, true>(p, s_pending, n_pend, s_ring, NWARPS * G::kWarpBytes);
-    GQA_STAMP(62);
     if (counted) decode_counters_release(p);
-    GQA_STAMP(63);
 }
 
 }  // namespace gqa_b200

@@ -278,13 +278,6 @@ mla_tc_merge_kernel(const MlaParams p) {
     }
 }
 
-#ifdef MLA_TC_STAMPS
-__device__ unsigned long long g_mla_stamps[160 * 64];
-#define MLA_STAMP(k) do { if (tid == 0 && (k) < 64) g_mla_stamps[blockIdx.x * 64 + (k)] = tc::global_timer_ns(); } while (0)
-#else
-#define MLA_STAMP(k) do {} while (0)
-#endif
-
 // grid (2 * pairs), cluster (2, 1, 1): persistent pairs that walk the schedule written by
 // mla_tc_plan_kernel (p.tc_sched).  p.page_shift = log2(page) or -1.
 template <typename T>
@@ -316,7 +309,6 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
 
     pdl_launch_dependents();
     pdl_wait();                                      // the schedule and the queries come from earlier kernels
-    MLA_STAMP(0);
     const uint32_t s_base = tc::smem_u32(smem);
     if (s_base & 1023u) {                            // the swizzled tiles need a 1024-byte aligned base
         if (tid == 0 && status) atomicExch(status, 3);
@@ -378,7 +370,6 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     __syncthreads();
     tc::cluster_sync_all();                          // both CTAs' barriers exist before any remote arrival
     tc::tc_fence_after();
-    MLA_STAMP(1);
     bool alive = true;
     int J0 = 0;                                      // running number of the item's first tile
     int item_no = 0;                                 // items of this pair so far
@@ -625,7 +616,6 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         const bool warp_live = quad < live_quads;
 
         if (warp_live) {
-        MLA_STAMP(2 + item_no * 6);
         // ---- latent part of Q_r: global -> registers -> tensor memory.  This thread writes half of
         //      its row (16 columns = 32 elements per step); rows past the last query row are zero ----
         {
@@ -655,7 +645,6 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             if (lane == 0) tc::mbar_arrive(bar_q);
         }
         if (st_pending) store_rows();                // the previous item's rows (see above)
-        MLA_STAMP(3 + item_no * 6);
 
         // this thread's 32 columns of the partial scores of tile t: TMEM -> registers -> landing
         // buffer t & 1 of the peer (once the peer has consumed tile t - 2 from it)
@@ -773,12 +762,9 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             if (lane == 0) tc::mbar_arrive(bar_p);
             // ---- the next tile's partial scores travel while the tensor cores take P(j) ----
             if (j + 1 < n_tiles) send_partial(J + 1);
-            if (j == 0) MLA_STAMP(4 + item_no * 6);
         }
-        MLA_STAMP(5 + item_no * 6);
         wait_bar(bar_empty + ((J0 + n_tiles - 1) % NS) * 8, ((J0 + n_tiles - 1) / NS) & 1);
         tc::tc_fence_after();
-        MLA_STAMP(6 + item_no * 6);
 
         // ---- row sum = the two halves, exchanged through shared memory by the live softmax warps
         //      (the landing buffers are not idle here: the peer may already send the next item's
@@ -794,7 +780,6 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         st_m = m_run;
         st_l = l_tot;
         st_pending = true;
-        MLA_STAMP(7 + item_no * 6);
         }   // live warps
     }
     J0 += n_tiles;
@@ -803,14 +788,12 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     }   // ranges of this pair
     if (st_pending) store_rows();                    // the last item's rows
     // ---- nobody leaves while the peer may still signal this CTA or write into it ----
-    MLA_STAMP(62);
     if (is_loader) cp_async_wait<0>();
     tc::tc_fence_before();
     __syncthreads();
     tc::cluster_sync_all();
     tc::tc_fence_after();
     if (warp == 0) tc::tmem_dealloc(tmem, kMlaTcTmemCols);
-    MLA_STAMP(63);
 }
 
 }  // namespace gqa_b200

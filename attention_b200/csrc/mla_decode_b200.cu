@@ -494,11 +494,4 @@ int mla_b200_tc_status(int reset) {
     return host;
 }
 
-#ifdef MLA_TC_STAMPS
-// temporary instrumentation: copy the cycle stamps of the last tensor-core attention launch
-GQA_B200_API int mla_b200_debug_stamps(unsigned long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_mla_stamps, sizeof(unsigned long long) * 160 * 64);
-}
-#endif
-
 }  // extern "C"

@@ -49,9 +49,11 @@ MIN_TIMED_MS = 50.0
 DTYPE_NAME = {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}
 
 # DRAM bytes (read + write) per decode-kernel launch from the ncu captures summarised under
-# profiles/, as a ratio to the algorithmic bytes of the captured case (the long-context
-# capture ran on a two-sequence cut of the workload; traffic grows in proportion to tokens).
-NCU_TRAFFIC_RATIO = {"c2_qwen3_8b_bf16": 1.010}
+# profiles/, as a ratio to the algorithmic bytes of the captured case (the long-context and
+# the skewed workload were captured on cuts to their first 2 and 64 sequences; traffic grows
+# in proportion to the tokens).
+NCU_TRAFFIC_RATIO = {"c2_qwen3_8b_bf16": 1.010, "c3_qwen25_7b_fp16": 1.013,
+                     "c4_longctx_bf16": 1.013, "c5_skewed_bf16": 1.010}
 
 
 def parse_args():
