@@ -416,7 +416,9 @@ def time_decode(attn, D, sampler, w, inputs, kw, K, W, spin_s):
             for _ in range(K):
                 out = call()
             marks[r + 1].record()
-        sampler.sample()            # at least one sample while the queue is still draining
+            sampler.sample()        # one sample per block from this thread as well (the sampling
+                                    # thread gets few turns while this loop holds the interpreter)
+        sampler.sample()            # and one while the queue is still draining
         torch.cuda.synchronize()
     D.barrier()
     clocks = sampler.summary()

@@ -43,8 +43,9 @@ extern "C" {
 #define GQA_B200_KERNEL_MMA 2  /* mma.sync m16n8k16; fp16/bf16, D in {64,128,256},
                                   16-byte aligned tensors                        */
 
-#define GQA_B200_KERNEL_TCGEN05 4 /* prefill only: tcgen05.mma with TMEM accumulators;
-                                  same shapes as GQA_B200_KERNEL_MMA               */
+#define GQA_B200_KERNEL_TCGEN05 4 /* prefill only: warp-specialised tcgen05.mma kernel
+                                  (persistent CTAs, accumulators, Q and P in tensor
+                                  memory); same shapes as GQA_B200_KERNEL_MMA      */
 
 /* status codes (negative = invalid argument) */
 #define GQA_B200_OK 0
