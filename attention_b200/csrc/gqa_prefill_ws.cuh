@@ -31,7 +31,7 @@
 //   k_empty[3]               tcgen05.commit: Q.K^T of the stage's tile done   -> loaders
 //   v_empty[3]               tcgen05.commit: P.V of the stage's tile done     -> loaders, softmax (O may be touched)
 //   bar_s[2]                 tcgen05.commit: scores of a tile are in TMEM     -> softmax
-//   bar_p                    8 warp arrivals: P is in TMEM, O rescaled        -> MMA lane
+//   bar_p[2]                 8 warp arrivals: P is in TMEM, O rescaled        -> MMA lane
 //   bar_q                    8 warp arrivals: the item's Q is in TMEM         -> MMA lane
 // Every wait is bounded (one second); a wait that runs out marks the CTA dead (later waits
 // give up at once), raises the status word, and the CTA still walks its protocol and frees
@@ -82,7 +82,7 @@ gqa_prefill_ws_kernel(const PrefillParams p, int* status) {
     static_assert(OC % 32 == 0, "output half rows are moved 32 columns at a time");
 
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ __align__(8) uint64_t s_bar[4 * NS + 4];
+    __shared__ __align__(8) uint64_t s_bar[4 * NS + 5];
     __shared__ uint32_t s_tmem;
     __shared__ int s_dead;
     __shared__ float s_max[2][2][kWsBM];             // [tile parity][column half][row]: half-row maxima
@@ -108,8 +108,8 @@ gqa_prefill_ws_kernel(const PrefillParams p, int* status) {
     const uint32_t v_full = tc::smem_u32(&s_bar[2 * NS]);
     const uint32_t v_empty = tc::smem_u32(&s_bar[3 * NS]);
     const uint32_t bar_s0 = tc::smem_u32(&s_bar[4 * NS]);          // [2]
-    const uint32_t bar_p = tc::smem_u32(&s_bar[4 * NS + 2]);
-    const uint32_t bar_q = tc::smem_u32(&s_bar[4 * NS + 3]);
+    const uint32_t bar_p = tc::smem_u32(&s_bar[4 * NS + 2]);       // [2], by tile parity
+    const uint32_t bar_q = tc::smem_u32(&s_bar[4 * NS + 4]);
 
     if (warp == 0) { tc::tmem_alloc(tc::smem_u32(&s_tmem), kWsTmemCols); tc::tmem_relinquish(); }
     if (tid == 0) {
@@ -120,7 +120,12 @@ gqa_prefill_ws_kernel(const PrefillParams p, int* status) {
         }
         tc::mbar_init(bar_s0, 1);
         tc::mbar_init(bar_s0 + 8, 1);
+        // (bar_p: two barriers used alternately.  A warp can be one tile ahead of another warp,
+        // and its next arrival must not count towards the phase the other is still in; it cannot
+        // be two ahead, because the scores of tile J + 2 are only issued once every warp's P(J)
+        // has arrived.)
         tc::mbar_init(bar_p, NT / 32);               // one arrival per softmax warp
+        tc::mbar_init(bar_p + 8, NT / 32);
         tc::mbar_init(bar_q, NT / 32);
         tc::fence_mbar_init();
         s_dead = 0;
@@ -266,7 +271,7 @@ gqa_prefill_ws_kernel(const PrefillParams p, int* status) {
                 if (n_tiles > 1) scores_of(1);
                 for (int j = 0; j < n_tiles; ++j) {
                     const int J = J0 + j, stage = J % NS;
-                    wait_bar(bar_p, J & 1);          // P(j) is in tensor memory, O rescaled
+                    wait_bar(bar_p + (J & 1) * 8, (J >> 1) & 1);   // P(j) is in tensor memory, O rescaled
                     wait_bar(v_full + stage * 8, (J / NS) & 1);
                     tc::fence_async_smem();
                     tc::tc_fence_after();
@@ -389,7 +394,7 @@ gqa_prefill_ws_kernel(const PrefillParams p, int* status) {
                 tc::tmem_st_wait();
                 tc::tc_fence_before();
                 __syncwarp();
-                if (lane == 0) tc::mbar_arrive(bar_p);
+                if (lane == 0) tc::mbar_arrive(bar_p + (J & 1) * 8);
             }
             wait_bar(v_empty + ((J0 + n_tiles - 1) % NS) * 8, ((J0 + n_tiles - 1) / NS) & 1);
             tc::tc_fence_after();

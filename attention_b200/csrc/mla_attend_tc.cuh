@@ -47,7 +47,7 @@
 //   full[3]    64 loader arrivals (when their copies land)   tile is in its stage   -> MMA lane
 //   empty[3]   tcgen05.commit   P.C of the stage's tile is done: stage and O are free
 //   bar_s[2]   tcgen05.commit   partial scores of a tile are in TMEM                -> softmax
-//   bar_p      8 warp arrivals  P is in TMEM, O rescaled                            -> MMA lane
+//   bar_p[2]   8 warp arrivals  P is in TMEM, O rescaled (even / odd tiles)         -> MMA lane
 //   bar_x[2]   transaction barriers: the peer's st.async stores complete 32 KB per tile
 //   bar_free[2] 8 remote warp arrivals   the peer has consumed a landing buffer of its own
 #pragma once
@@ -263,7 +263,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     constexpr int HC = BN / 2;                       // score columns per softmax thread
 
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ __align__(8) uint64_t s_bar[2 * NS + NSB + 6];
+    __shared__ __align__(8) uint64_t s_bar[2 * NS + NSB + 7];
     __shared__ uint32_t s_tmem;
     __shared__ int s_dead;
     __shared__ float s_max[2][2][kMlaTcRows];        // [tile parity][column half][row]: half-row maxima
@@ -294,6 +294,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
     const uint32_t bar_x = tc::smem_u32(&s_bar[2 * NS + NSB + 1]);      // [2], one per landing buffer
     const uint32_t bar_free = tc::smem_u32(&s_bar[2 * NS + NSB + 3]);   // [2]
     const uint32_t bar_q = tc::smem_u32(&s_bar[2 * NS + NSB + 5]);
+    const uint32_t bar_p1 = tc::smem_u32(&s_bar[2 * NS + NSB + 6]);     // bar_p of the odd tiles
 
     if (warp == 0) { tc::tmem_alloc(tc::smem_u32(&s_tmem), kMlaTcTmemCols); tc::tmem_relinquish(); }
     if (tid == 0) s_dead = 0;
@@ -327,7 +328,11 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         for (int i = 0; i < NS; ++i) { tc::mbar_init(bar_full + i * 8, NL); tc::mbar_init(bar_empty + i * 8, 1); }
 #pragma unroll
         for (int i = 0; i < NSB; ++i) tc::mbar_init(bar_s0 + i * 8, 1);
+        // (two barriers used alternately: a warp can be one tile ahead of another warp, and its
+        // next arrival must not count towards the phase the other is still in; it cannot be two
+        // ahead, because the scores of tile J + 2 are only issued once every warp's P(J) has arrived)
         tc::mbar_init(bar_p, live_warps);            // one arrival per live softmax warp
+        tc::mbar_init(bar_p1, live_warps);
         tc::mbar_init(bar_q, live_warps);
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -568,7 +573,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             scores_of(0);                            // (the rotated block of Q_r rides on the first tile's barrier)
             if (n_tiles > 1) scores_of(1);
             for (int j = 0; j < n_tiles; ++j) {
-                wait_bar(bar_p, (J0 + j) & 1);       // P(j) is in tensor memory, O rescaled
+                wait_bar(((J0 + j) & 1) ? bar_p1 : bar_p, ((J0 + j) >> 1) & 1);   // P(j) is in tensor memory, O rescaled
                 tc::tc_fence_after();
                 issue_pv(j);
                 // S(j+2) reuses the buffer of S(j) / P(j): P.C(j) is queued ahead of it and the tensor
@@ -731,7 +736,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
             tc::tmem_st_wait();
             tc::tc_fence_before();
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive(bar_p);
+            if (lane == 0) tc::mbar_arrive((J & 1) ? bar_p1 : bar_p);
             // ---- the next tile's partial scores travel while the tensor cores take P(j) ----
             if (j + 1 < n_tiles) send_partial(J + 1);
         }
