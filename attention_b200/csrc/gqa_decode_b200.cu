@@ -16,7 +16,7 @@
 #include "gqa_plan_merge.cuh"
 #include "gqa_prefill_mma.cuh"
 #include "gqa_prefill_simt.cuh"
-#include "gqa_prefill_ws.cuh"
+#include "gqa_prefill_pp.cuh"
 #include "kv_append.cuh"
 
 using namespace gqa_b200;
@@ -752,20 +752,20 @@ cudaError_t prefill_tc_status_address(int** out) {
 }
 
 template <typename T, int D>
-cudaError_t launch_prefill_ws(const PrefillParams& p, cudaStream_t stream) {
+cudaError_t launch_prefill_pp(const PrefillParams& p, cudaStream_t stream) {
     DeviceInfo* dev = nullptr;
     cudaError_t e = device_info(&dev);
     if (e != cudaSuccess) return e;
-    const size_t smem = PrefillWsGeom<D>::kSmemBytes;
+    const size_t smem = PrefillPpGeom<D>::kSmemBytes;
     int per_sm = 0;   // the first call also raises the kernel's dynamic shared-memory limit
-    e = resident_ctas(gqa_prefill_ws_kernel<T, D>, kWsThreads, smem, dev->max_smem_optin, &per_sm);
+    e = resident_ctas(gqa_prefill_pp_kernel<T, D>, kPpThreads, smem, dev->max_smem_optin, &per_sm);
     if (e != cudaSuccess) return e;
     int* status = nullptr;
     e = prefill_tc_status_address(&status);
     if (e != cudaSuccess) return e;
-    const long long items = (long long)((p.tq + kWsBM - 1) / kWsBM) * p.q_heads * p.batch;
+    const long long items = (long long)((p.tq + 2 * kPpBM - 1) / (2 * kPpBM)) * p.q_heads * p.batch;
     const unsigned grid = (unsigned)(items < dev->sm_count ? items : dev->sm_count);   // persistent: one CTA per SM
-    gqa_prefill_ws_kernel<T, D><<<grid, kWsThreads, smem, stream>>>(p, status);
+    gqa_prefill_pp_kernel<T, D><<<grid, kPpThreads, smem, stream>>>(p, status);
     return cudaGetLastError();
 }
 
@@ -773,8 +773,8 @@ template <typename T>
 cudaError_t launch_prefill_t(const PrefillParams& p, bool use_mma, bool use_tc, cudaStream_t stream) {
     if (use_tc) {
         if constexpr (sizeof(T) == 2) {
-            if (p.head_dim == 64) return launch_prefill_ws<T, 64>(p, stream);
-            return launch_prefill_ws<T, 128>(p, stream);
+            if (p.head_dim == 64) return launch_prefill_pp<T, 64>(p, stream);
+            return launch_prefill_pp<T, 128>(p, stream);
         } else {
             return cudaErrorInvalidValue;
         }

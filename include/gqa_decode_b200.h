@@ -44,8 +44,9 @@ extern "C" {
                                   16-byte aligned tensors                        */
 
 #define GQA_B200_KERNEL_TCGEN05 4 /* prefill only: warp-specialised tcgen05.mma kernel
-                                  (persistent CTAs, accumulators, Q and P in tensor
-                                  memory); same shapes as GQA_B200_KERNEL_MMA      */
+                                  (persistent CTAs, two query tiles per CTA, scores,
+                                  P and accumulators in tensor memory); same shapes
+                                  as GQA_B200_KERNEL_MMA                            */
 
 /* status codes (negative = invalid argument) */
 #define GQA_B200_OK 0
