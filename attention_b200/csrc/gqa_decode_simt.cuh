@@ -81,6 +81,10 @@ gqa_decode_simt_kernel(const DecodeParams p) {
     FusedPlan plan;
     plan.base = p.chunk_base;
     plan.total_chunks = 0;
+    // the first item number is asked for before the plan, so the counter's answer travels
+    // while the plan is computed
+    int first_item = 0;
+    if (counted && tid == 0) first_item = atomicAdd(p.hdr + kHdrCounter, 1);
     int n_items;
     if (fused) {
         plan = fused_plan<NW * 32>(p, s_off, s_red);
@@ -93,7 +97,7 @@ gqa_decode_simt_kernel(const DecodeParams p) {
     int n_pend = 0;     // one-launch mode: multi-chunk items whose tickets are still to be taken
     int item;
     if (counted) {
-        if (tid == 0) s_item = atomicAdd(p.hdr + kHdrCounter, 1);
+        if (tid == 0) s_item = first_item;
         __syncthreads();
         item = s_item;
     } else {
