@@ -1,6 +1,6 @@
 // Dense GQA prefill on the 5th-generation tensor cores: fp16 / bf16, head_dim 64 / 128.
 // Persistent CTAs (one per SM) walk the work items (batch, query head, 256 query rows),
-// heaviest first.  An item is two tiles of 128 query rows, A and B, that share every K and V
+// heaviest first, in alternating CTA order from round to round.  An item is two tiles of 128 query rows, A and B, that share every K and V
 // tile; a K/V tile of 128 keys is worked on in two halves of 64 keys (h = 0, 1):
 //
 //   S_X(j,h)[128 x 64] = Q_X[128 x D] . K(j)[64 h .. 64 h + 63][D]^T   A = Q_X from shared memory, B = K rows (K-major)
@@ -189,7 +189,13 @@ gqa_prefill_pp_kernel(const PrefillParams p, int* status) {
     int JX0 = 0;                                     // softmax warps: running tile number of their query tile
     int JA0 = 0, JB0 = 0;                            // MMA lane: the same for A and B
     int item_no = 0;                                 // items with tiles this CTA has started
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    // Round k hands items k * grid .. (k + 1) * grid - 1 to the CTAs, in CTA order in even rounds
+    // and in reverse order in odd ones: the items get lighter with their number, and a CTA that
+    // always took the i-th of a round would end 6 - 7 % (T 4096 .. 16384) above the mean.
+    for (int round = 0; round * (int)gridDim.x < n_items; ++round) {
+        const int item = round * (int)gridDim.x +
+                         ((round & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
+        if (item >= n_items) continue;
         const int qt = n_qt - 1 - item / per_qt;
         const int rem = item - (item / per_qt) * per_qt;
         const int b = rem / p.q_heads, h = rem - b * p.q_heads;
