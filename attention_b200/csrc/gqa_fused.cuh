@@ -45,11 +45,12 @@ __device__ __forceinline__ int fused_chunks_for(int len, int base) {
 //   the partial written and read back)  +  the expected idle tail at the end of the kernel,
 //   about half of the longest item when CTAs pull items from a counter.
 // The base with the lowest estimate wins; a base whose chunk total does not fit the
-// workspace is not considered.  The two constants were fitted to measured kernel times of
-// the benchmark workloads at explicit bases 1024 .. 128 (group 4 to 8, bf16 / fp16, D 128):
-// halving the base costs about 0.5 us per extra item per CTA and shortens the tail by half
-// an item.
-constexpr float kFusedItemOverheadTokens = 64.f;
+// workspace is not considered.  The two constants were fitted to measured call times at
+// explicit bases 1024 .. 64 of the benchmark workloads (group 4 to 8, bf16 / fp16 / fp32, D 128)
+// and of the quarter and the eighth of the skewed batch that one GPU of four or eight decodes:
+// with 96 tokens per item every one of them gets its fastest base (with 64 the eighth, 2 - 6
+// items per CTA, was cut at 256 and ran 66.8 us instead of 57.4).
+constexpr float kFusedItemOverheadTokens = 96.f;
 constexpr float kFusedTailFraction = 0.5f;
 
 __device__ __forceinline__ int fused_pick_base(const int (&cnt)[kNumAutoBases], const int (&longest)[kNumAutoBases],
