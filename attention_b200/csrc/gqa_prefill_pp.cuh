@@ -161,6 +161,7 @@ gqa_prefill_pp_kernel(const PrefillParams p, int* status) {
         if (status) atomicExch(status, 2);
     };
     auto wait_bar = [&](uint32_t bar, uint32_t parity) {
+        if (tc::mbar_test(bar, parity)) return;      // already there: no look at the dead flag, no timer
         if (!tc::mbar_wait(bar, parity, s_dead ? 1000ull : 1000000000ull)) timed_out();
     };
 

@@ -126,16 +126,6 @@ __device__ __forceinline__ void mbar_arrive_remote_relaxed(uint32_t cluster_addr
 __device__ __forceinline__ void mbar_inval(uint32_t bar) {
     asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
-// one non-blocking test of a barrier phase
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    return done != 0;
-}
 // mbar_wait with cluster-scope acquire: orders the peer CTA's stores before the reads that follow.
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, uint64_t max_ns) {
     uint64_t start = 0;
@@ -462,6 +452,7 @@ mla_attend_tc_kernel(const MlaParams p, int* status) {
         if (status) atomicExch(status, 2);
     };
     auto wait_bar = [&](uint32_t bar, uint32_t parity) {
+        if (tc::mbar_test(bar, parity)) return;      // already there: no look at the dead flag, no timer
         if (!tc::mbar_wait(bar, parity, s_dead ? 1000ull : 1000000000ull)) timed_out();
     };
     auto wait_bar_cluster = [&](uint32_t bar, uint32_t parity) {
