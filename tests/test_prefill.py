@@ -179,3 +179,23 @@ def test_prefill_kernels_agree_on_a_large_ragged_batch():
     want = gqa_oracle.reference_gqa_prefill(*args)
     for kernel in ("tcgen05", "mma"):
         _close(attn.gqa_prefill(*args, kernel=kernel), want, torch.bfloat16, kernel)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("causal", [True, False])
+def test_prefill_two_tile_item_edges(causal):
+    """The tcgen05 kernel works on items of two 128-row query tiles: query lengths around 128,
+    256 and 384 rows (second tile empty, one row, full), keys shorter than queries (the first
+    rows of a causal sequence see nothing), keys around the 64-key half tiles, and enough
+    (sequence, head) pairs that a CTA walks several items in both directions of the hand-out."""
+    q_lens = [255, 256, 257, 128, 129, 384, 385, 512, 1, 300, 200, 400]
+    kv_lens = [255, 300, 257, 64, 65, 127, 500, 129, 193, 100, 200, 40]
+    args = _case(12, 512, 500, 16, 4, 128, torch.bfloat16, q_lens, kv_lens, seed=21)
+    want = gqa_oracle.reference_gqa_prefill(*args, causal=causal)
+    for kernel in ("tcgen05", "mma"):
+        got = attn.gqa_prefill(*args, causal=causal, kernel=kernel)
+        _close(got, want, torch.bfloat16, f"causal={causal} {kernel}")
+        for b, n in enumerate(q_lens):
+            assert torch.count_nonzero(got[b, n:]) == 0, f"rows past q_len of sequence {b} ({kernel})"
+    from attention_b200 import _cabi
+    assert _cabi.load().gqa_b200_prefill_tc_status(0) == 0
