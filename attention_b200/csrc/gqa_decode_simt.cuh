@@ -143,9 +143,6 @@ gqa_decode_simt_kernel(const DecodeParams p) {
                 __syncthreads();   // previous segment's table no longer in use
                 stage_table(p, w.b, s0, s1, s_table, first_page);
                 __syncthreads();
-                // rows of the warp's next TOK tokens are requested before the current ones are
-                // used (register double buffer): an item of a few iterations is otherwise a chain
-                // of dependent memory round trips
                 auto load_tokens = [&](int tb, float (&kx)[TOK][EPL], float (&vx)[TOK][EPL], bool (&valid)[TOK]) {
 #pragma unroll
                     for (int tk = 0; tk < TOK; ++tk) {
@@ -165,20 +162,13 @@ gqa_decode_simt_kernel(const DecodeParams p) {
                         }
                     }
                 };
-                float kn[TOK][EPL], vn[TOK][EPL];
-                bool validn[TOK];
-                int tb = s0 + warp * TOK;
-                if (tb < s1) load_tokens(tb, kn, vn, validn);
-                for (; tb < s1; tb += NW * TOK) {
+                // (requesting the next TOK rows ahead of use, a register double buffer, was tried for
+                // the few-iteration items of small batches: no gain there, and its registers cost a
+                // resident CTA per SM on large ones: 779 against 620 us on batch 64 x 1-4 k tokens)
+                for (int tb = s0 + warp * TOK; tb < s1; tb += NW * TOK) {
                     float kx[TOK][EPL], vx[TOK][EPL];
                     bool valid[TOK];
-#pragma unroll
-                    for (int tk = 0; tk < TOK; ++tk) {
-                        valid[tk] = validn[tk];
-#pragma unroll
-                        for (int j = 0; j < EPL; ++j) { kx[tk][j] = kn[tk][j]; vx[tk][j] = vn[tk][j]; }
-                    }
-                    if (tb + NW * TOK < s1) load_tokens(tb + NW * TOK, kn, vn, validn);
+                    load_tokens(tb, kx, vx, valid);
 #pragma unroll
                     for (int g = 0; g < GB; ++g) {
                         if (g >= rows_valid) continue;
