@@ -123,9 +123,6 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive_remote_relaxed(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-__device__ __forceinline__ void mbar_inval(uint32_t bar) {
-    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
 // mbar_wait with cluster-scope acquire: orders the peer CTA's stores before the reads that follow.
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, uint64_t max_ns) {
     uint64_t start = 0;
